@@ -1,0 +1,154 @@
+// Plain structs shared by the host launcher (C++) and the device code (CUDA).
+// Everything here is POD so that it can cross the thin C ABI between them.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  FDMOE_MAX_WORLD = 8,
+  FDMOE_MAX_TOPK = 8,
+  FDMOE_MAX_EXPERTS = 128,
+  FDMOE_TILE_M = 128,    // rows of one expert's packed buffer per GEMM tile
+  FDMOE_TILE_N1 = 128,   // FFN1: activation columns per tile (MMA N = 2 * 128: gate + up)
+  FDMOE_TILE_N2 = 256,   // FFN2: hidden columns per tile
+  FDMOE_TILE_K = 64,     // one 128-byte swizzle atom of bf16 per stage
+  FDMOE_GATE_TOKENS = 32,  // tokens per gate tile
+};
+
+// Task kinds held by the global work queue.
+enum {
+  FDMOE_TASK_NONE = 0,
+  FDMOE_TASK_FFN1 = 1,     // (expert, m_tile, n_tile, rows): SwiGLU tile
+  FDMOE_TASK_FFN2 = 2,     // (expert, m_tile, n_tile, rows): down-projection tile
+  FDMOE_TASK_COMBINE = 3,  // (token group): ordered sum over the K slots
+  FDMOE_TASK_FLUSH = 4,    // all ranks finished their gate phase: publish remaining tiles
+  FDMOE_TASK_TESTA = 5,    // task-system self test: x[i] *= 2 over a chunk, then push TESTB
+  FDMOE_TASK_TESTB = 6,    // task-system self test: x[i] += 1 over a chunk
+  FDMOE_TASK_EXIT = 7,
+};
+
+// Status codes written by the kernel (first error wins).
+enum {
+  FDMOE_OK = 0,
+  FDMOE_ERR_TIMEOUT_QUEUE = 1,   // a worker waited too long for its ticket
+  FDMOE_ERR_TIMEOUT_RING = 2,    // CTA-internal task ring
+  FDMOE_ERR_TIMEOUT_STAGE = 3,   // TMA/MMA shared-memory stage barrier
+  FDMOE_ERR_TIMEOUT_TMEM = 4,    // accumulator hand-off barrier
+  FDMOE_ERR_TIMEOUT_PEER = 5,    // a peer rank never signalled readiness
+  FDMOE_ERR_QUEUE_OVERFLOW = 6,
+  FDMOE_ERR_BAD_TASK = 7,
+  FDMOE_ERR_ROW_OVERFLOW = 8,    // more rows for an expert than its buffer holds
+};
+
+// One slot of the ticket queue (16 bytes).  `seq` == ticket + 1 once the slot
+// holds the task of that ticket.
+typedef struct {
+  uint32_t seq;
+  uint32_t a;  // kind | expert << 8 | n_tile << 20
+  uint32_t b;  // m_tile, or token group, or chunk index
+  uint32_t c;  // valid rows in the tile
+} FdmoeSlot;
+
+// Sideband of one packed row (16 bytes): where its result goes.
+typedef struct {
+  int32_t token;      // index of the token on its home rank
+  int32_t home_slot;  // home rank << 8 | slot k
+  float weight;       // routing weight of (token, slot)
+  int32_t pad;
+} FdmoeRowMeta;
+
+// Per-rank control block.  Lives in the rank's symmetric arena so that peers
+// can reach it.  Fields on separate 128-byte lines are written by different
+// agents.
+typedef struct {
+  // --- persistent queue state (never zeroed between launches)
+  uint32_t q_head;
+  uint32_t pad0[31];
+  uint32_t q_tail;
+  uint32_t pad1[31];
+  uint32_t closed;  // 0 running, 1 finished, 2 aborted
+  uint32_t status;  // first error code
+  uint32_t status_info;
+  uint32_t exit_cnt;
+  uint32_t pad2[28];
+  uint32_t ready[32];  // ready[r] = launch epoch of peer r (written by peer r)
+  // --- per-launch counters: [launch_begin, launch_end) is zeroed before each launch
+  uint32_t launch_begin;
+  uint32_t gate_next;        // next gate tile to claim
+  uint32_t gate_done;        // gate tiles finished on this rank
+  uint32_t ranks_done;       // ranks whose gate phase is finished (incl. this one)
+  uint32_t flush_done;
+  uint32_t mtiles_total;     // m-tiles of this rank's experts this launch
+  uint32_t mtiles_done;      // m-tiles whose FFN2 is complete
+  uint32_t tokens_combined;
+  uint32_t tokens_launch;    // tokens of this rank this launch (written at kernel start)
+  uint32_t executed;         // tasks finished (used only with expected_static)
+  uint32_t pad3[22];
+} FdmoeCtl;
+
+// What one rank can reach of a peer (or of itself): all device pointers valid
+// in this process.
+typedef struct {
+  FdmoeCtl* ctl;
+  FdmoeSlot* slots;
+  uint32_t* expert_cnt;    // [El]       rows allocated per local expert
+  uint32_t* tile_landed;   // [El * MT]  rows landed per (expert, m_tile)
+  uint32_t* tok_arrivals;  // [groups]   rows returned per token group
+  void* packed;            // bf16 [El * cap_rows, H]
+  FdmoeRowMeta* meta;      // [El * cap_rows]
+  void* ystage;            // bf16 [max_tokens, K, H]
+} FdmoePeer;
+
+// 128-byte opaque TMA descriptor (CUtensorMap), kept as raw words so that this
+// header does not need cuda.h.
+typedef struct __attribute__((aligned(64))) {
+  uint64_t opaque[16];
+} FdmoeTensorMap;
+
+typedef struct {
+  FdmoeTensorMap tm_packed;  // [El*cap_rows, H]   box 64 x 128
+  FdmoeTensorMap tm_w13;     // [El*2I, H]         box 64 x 128
+  FdmoeTensorMap tm_act;     // [El*cap_rows, I]   box 64 x 128
+  FdmoeTensorMap tm_w2;      // [El*H, I]          box 64 x 256
+
+  FdmoePeer peers[FDMOE_MAX_WORLD];  // peers[rank] is this rank itself
+
+  // shape
+  int32_t H, I, E, K, El;
+  int32_t world, rank;
+  int32_t T;            // tokens this launch
+  int32_t cap_rows;     // rows per expert buffer (multiple of 128)
+  int32_t MT;           // cap_rows / 128
+  int32_t queue_mask;   // capacity - 1 (capacity is a power of two)
+  int32_t combine_group;  // tokens per COMBINE task
+  int32_t eager;        // publish full tiles as they land instead of at flush
+  int32_t mode;         // 0 full layer; 1 stop after gate; 2 static tasks only (no gate)
+  uint32_t expected_static;  // mode 2: tasks pre-filled by the host
+  uint32_t epoch;       // launch counter (identical on all ranks)
+  uint64_t timeout_ns;  // budget of every device-side wait
+
+  const void* x;        // bf16 [T, H]
+  void* out;            // bf16 [T, H] (may alias x)
+  const void* gate_w;   // bf16 [E, H]
+  void* act;            // bf16 [El * cap_rows, I]
+  int32_t* topk_idx;    // [max_tokens, K]
+  float* topk_w;        // [max_tokens, K]
+  uint32_t* ffn1_done;  // [El * MT]
+  uint32_t* ffn2_done;  // [El * MT]
+  uint32_t* status_host;  // mapped pinned word: first error code, readable without a sync
+  int32_t* test_buf;    // task-system self test payload
+} FdmoeParams;
+
+// Thin C ABI between the C++ host launcher and the CUDA translation unit.
+// All functions return a cudaError_t value as int.
+int fdmoe_kernel_prepare(int* smem_bytes_out, int* grid_out);
+int fdmoe_kernel_launch(const FdmoeParams* params, int grid, void* stream);
+int fdmoe_cast_f32_to_bf16(const float* src, void* dst, uint64_t n, void* stream);
+int fdmoe_cast_bf16_to_f32(const void* src, float* dst, uint64_t n, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
