@@ -1,0 +1,342 @@
+#!/usr/bin/env python
+"""MoE-layer throughput benchmark (tokens/s) for the B200 FlashDMoE launcher.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A step is one `Launch` of the layer over one batch of synthetic tokens (seeded N(0,1) bf16
+activations, N(0,0.02) bf16 weights; real Qwen3 checkpoints are not available offline).  Default
+workload: the Qwen3-30B-A3B layer shape (hidden 2048, 128 experts, top-8, intermediate 768) at 4096
+tokens per GPU; with N > 1 the experts are sharded over the ranks (expert parallelism) and the
+tokens per GPU stay fixed (weak scaling).  Rank 0 prints ONE JSON line.
+
+`--impl reference` times the reference project's own CPU MoE (oracle/_ref when it was built from
+the reference sources, else the C restatement under oracle/) on the host cores, on a bounded sample
+of the same workload per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from flash_distributed_moe_b200 import synth  # noqa: E402
+
+SHAPES = {"30b": synth.QWEN3_30B_A3B, "235b": synth.QWEN3_235B_A22B}
+L2_BYTES = 126e6
+
+
+def flops_per_token(s) -> float:
+    return 2.0 * s.hidden * s.experts + s.topk * 6.0 * s.hidden * s.inter
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) in a background thread
+    while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.001):
+        import threading
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            phys = index
+            if visible:
+                ids = [v.strip() for v in visible.split(",") if v.strip()]
+                if index < len(ids) and ids[index].isdigit():
+                    phys = int(ids[index])
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+            return
+        self._period = period_s
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def _run(self):
+        nv = self._nv
+        flags = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "sw_power_cap": 0x4}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                r = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                for name, bit in flags.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self._period)
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def make_gpu_inputs(shape, tokens, rank, world, device):
+    """Weights and tokens generated on the device from fixed seeds (bf16)."""
+    el = shape.experts // world
+    g = torch.Generator(device=device).manual_seed(0)
+    gate = (torch.randn(shape.experts, shape.hidden, generator=g, device=device) * 0.02).to(torch.bfloat16)
+    ge = torch.Generator(device=device).manual_seed(1000 + rank)
+    w13 = (torch.randn(el, 2 * shape.inter, shape.hidden, generator=ge, device=device) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn(el, shape.hidden, shape.inter, generator=ge, device=device) * 0.02).to(torch.bfloat16)
+    gt = torch.Generator(device=device).manual_seed(7 + rank)
+    x = torch.randn(tokens, shape.hidden, generator=gt, device=device).to(torch.bfloat16)
+    return gate, w13, w2, x
+
+
+def cpu_reference_run(oracle, xf, gf, w13f, w2f, topk, threads):
+    t0 = time.perf_counter()
+    if oracle.kind == "reference":
+        out = oracle.full_moe(xf, gf, w13f, w2f, topk, threads=threads)
+    else:
+        out = oracle.full_moe(xf, gf, w13f, w2f, topk, threads=threads)
+    return out, time.perf_counter() - t0
+
+
+def cpu_baseline_leg(shape, gate, w13, w2, x, gpu_out, budget_s=15.0):
+    """Times the CPU reference on a bounded sample of the step's tokens (all host threads) and uses its
+    results to check the GPU output of those tokens.  This is the only place the b200 arm touches oracle/."""
+    from oracle import cpu_oracle
+    cpu_oracle.build()
+    oracle = cpu_oracle.best_oracle()
+    threads = oracle.max_threads()
+    gf = gate.float().cpu().numpy()
+    w13f = w13.float().cpu().numpy()
+    w2f = w2.float().cpu().numpy()
+    xs = x.float().cpu().numpy()
+    probe = min(threads, xs.shape[0])
+    _, dt = cpu_reference_run(oracle, xs[:probe], gf, w13f, w2f, shape.topk, threads)
+    per_round = max(dt, 1e-3)
+    n = int(min(xs.shape[0], max(probe, probe * (budget_s / per_round))))
+    ref, dt = cpu_reference_run(oracle, xs[:n], gf, w13f, w2f, shape.topk, threads)
+    got = gpu_out[:n].float().cpu().numpy()
+    err = np.abs(got - ref)
+    parity = {"tokens_checked": n, "max_abs": float(err.max()),
+              "rel_l2": float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30)),
+              "tolerance": {"max_abs": 2e-2, "rel_l2": 1e-2}}
+    parity["pass"] = bool(parity["max_abs"] <= 2e-2 and parity["rel_l2"] <= 1e-2)
+    base = {"value": n / dt, "unit": "tokens/s", "cores": threads, "kind": oracle.kind,
+            "sample": f"first {n} tokens of the step's batch, fp32, all host threads, {dt:.1f} s"}
+    return base, parity
+
+
+def run_reference_arm(args, shape):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    from oracle import cpu_oracle
+    cpu_oracle.build()
+    oracle = cpu_oracle.best_oracle()
+    threads = oracle.max_threads()
+    gate, w13, w2 = synth.make_weights(shape, seed=0)
+    x = synth.make_tokens(shape, max(threads * 4, 64), seed=0)
+    gf, w13f, w2f, xf = [t.float().numpy() for t in (gate, w13, w2, x)]
+    # bounded sample per step: calibrate one round of `threads` tokens, then size the step so that the
+    # whole run stays within about two minutes
+    _, dt = cpu_reference_run(oracle, xf[:threads], gf, w13f, w2f, shape.topk, threads)
+    total_steps = args.steps + args.warmup
+    per_step_budget = max(0.5, 120.0 / max(total_steps, 1))
+    n = int(min(xf.shape[0], max(threads, threads * int(per_step_budget / max(dt, 1e-3)))))
+    for _ in range(args.warmup):
+        cpu_reference_run(oracle, xf[:n], gf, w13f, w2f, shape.topk, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_reference_run(oracle, xf[:n], gf, w13f, w2f, shape.topk, threads)
+    dt = (time.perf_counter() - t0) / max(args.steps, 1)
+    value = n / dt
+    sample = f"{n} tokens per step of the {args.tokens}-token batch, fp32, {threads} host threads"
+    line = {
+        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{shape.name} MoE layer, {args.tokens} tokens per GPU (CPU: sampled)",
+                   "hidden": shape.hidden, "experts": shape.experts, "topk": shape.topk, "inter": shape.inter},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": oracle.kind, "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--shape", default="30b", choices=sorted(SHAPES))
+    ap.add_argument("--tokens", type=int, default=4096, help="tokens per GPU per step")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    shape = SHAPES[args.shape]
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    if args.impl == "reference":
+        run_reference_arm(args, shape)
+        return
+
+    rank, world, local = dist_env()
+    if world != args.gpus:
+        if args.gpus != 1 or world != 1:
+            raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run)")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+
+    from flash_distributed_moe_b200 import MoeKernelLauncher
+    import torch.distributed as dist
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+
+    T = args.tokens
+    gate, w13, w2, x = make_gpu_inputs(shape, T, rank, world, device)
+    launcher = MoeKernelLauncher()
+    if world > 1:
+        box = [MoeKernelLauncher.getDistributedUniqueId() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        uid = box[0]
+    else:
+        uid = MoeKernelLauncher.getDistributedUniqueId(empty=True)
+    launcher.create(gate, w13, w2, T, uid, rank, world, topk=shape.topk)
+    out = torch.empty_like(x)
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(device)
+
+    for _ in range(args.warmup):
+        launcher.launch(x, out)
+    barrier()
+    code, info = launcher.last_status()
+    if code != 0:
+        raise SystemExit(f"device-side error {code} (info 0x{info:x}) during warm-up")
+
+    # ---- device-resident timing: K launches, one event pair per launch (inputs stay in HBM; the
+    # 1.2 GB of expert weights read each step is larger than L2, so no flush is needed)
+    sampler = ClockSampler(local) if rank == 0 else None
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    t_begin = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_begin.record()
+    for i in range(args.steps):
+        starts[i].record()
+        launcher.launch(x, out)
+        stops[i].record()
+    t_end.record()
+    barrier()
+    total_ms = t_begin.elapsed_time(t_end)
+    per_launch_ms = [s.elapsed_time(e) for s, e in zip(starts, stops)]
+    code, info = launcher.last_status()
+    if code != 0:
+        raise SystemExit(f"device-side error {code} (info 0x{info:x}) during the timed region")
+
+    # ---- end to end through the host-buffer entry point: pinned host tokens in, pinned host result out
+    h_in = x.cpu().pin_memory()
+    h_out = torch.empty_like(h_in).pin_memory()
+    for _ in range(2):
+        launcher.launch_host(h_in, h_out)
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        launcher.launch_host(h_in, h_out)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None  # covers both timed regions
+    e2e_ok = torch.equal(h_out, out.cpu())
+
+    if world > 1:
+        t = torch.tensor([total_ms, e2e_ms, max(per_launch_ms), statistics.mean(per_launch_ms)], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms, _, mean_launch_ms = [float(v) for v in t.tolist()]
+    else:
+        mean_launch_ms = statistics.mean(per_launch_ms)
+
+    result = None
+    if rank == 0:
+        peaks = measured_peaks()
+        tokens_total = T * world
+        ms_per_step = total_ms / args.steps
+        value = tokens_total / (ms_per_step * 1e-3)
+        flop_launch = flops_per_token(shape) * T  # per GPU under uniform routing
+        achieved_tflops = flop_launch / (mean_launch_ms * 1e-3) / 1e12
+        weight_bytes = (shape.experts // world) * 3 * shape.hidden * shape.inter * 2
+        act_bytes = T * shape.hidden * 2 * (2 + 2 * shape.topk * 2) + T * shape.topk * shape.inter * 2 * 2
+        hbm_gbs = (weight_bytes + act_bytes) / (mean_launch_ms * 1e-3) / 1e9
+        result = {
+            "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{shape.name} MoE layer, {T} tokens per GPU, top-{shape.topk} of {shape.experts} "
+                                   f"experts, random gate, experts sharded over {world} GPU(s)",
+                       "hidden": shape.hidden, "inter": shape.inter, "tokens_per_gpu": T,
+                       "l2_policy": "inputs larger than L2 (expert weights read per step exceed 126 MB)"},
+            "roofline": {"bound": "tensor", "achieved": achieved_tflops, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": achieved_tflops / peaks["bf16_tflops"], "traffic": None,
+                         "peak_source": peaks["source"] + " burst",
+                         "kernel": "moe_persistent_kernel", "kernel_ms": mean_launch_ms,
+                         "hbm_algorithmic_gbs": hbm_gbs, "hbm_frac_of_" + peaks["source"]: hbm_gbs / peaks["hbm_gbs"]},
+            "e2e": {"value": tokens_total / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": int(h_in.numel() * 2), "d2h_bytes_per_step": int(h_out.numel() * 2),
+                    "matches_device_path": bool(e2e_ok)},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            base, parity = cpu_baseline_leg(shape, gate, w13, w2, x, out)
+            result["cpu_baseline"] = base
+            result["parity"] = parity
+    launcher.destroy()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -186,6 +186,7 @@ class MoeKernelLauncher final : public moe::IMoeKernelLauncher {
   void *tok_bf16_ = nullptr, *out_bf16_ = nullptr;
   // host-buffer entry point staging
   void *host_in_dev_ = nullptr, *host_out_dev_ = nullptr;
+  uint32_t* prof_ = nullptr;  // optional event trace (FLASHMOE_PROFILE=1)
   Bootstrap boot_;
   bool inited_ = false;
 };
@@ -195,7 +196,7 @@ void MoeKernelLauncher::FreeAll() {
     if (r != rank_ && peer_bases_[r]) cudaIpcCloseMemHandle(peer_bases_[r]);
   peer_bases_.clear();
   void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, gate_bf16_, w13_bf16_, w2_bf16_,
-                  tok_bf16_, out_bf16_, host_in_dev_, host_out_dev_};
+                  tok_bf16_, out_bf16_, host_in_dev_, host_out_dev_, prof_};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   arena_ = nullptr;
@@ -203,6 +204,7 @@ void MoeKernelLauncher::FreeAll() {
   topk_idx_ = nullptr;
   topk_w_ = nullptr;
   gate_bf16_ = w13_bf16_ = w2_bf16_ = tok_bf16_ = out_bf16_ = host_in_dev_ = host_out_dev_ = nullptr;
+  prof_ = nullptr;
   if (status_host_) cudaFreeHost(status_host_);
   status_host_ = nullptr;
   boot_.Close();
@@ -397,6 +399,12 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   params_.ffn1_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn1_done);
   params_.ffn2_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn2_done);
   params_.status_host = status_dev_;
+  if (EnvInt("FLASHMOE_PROFILE", 0)) {
+    const size_t bytes = (size_t)grid_ * FDMOE_PROF_EVENTS * 16;
+    CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&prof_), bytes));
+    CUDA_ERROR_CHECK(cudaMemsetAsync(prof_, 0, bytes, stream));
+    params_.prof = prof_;
+  }
 
   CUDA_ERROR_CHECK(cudaStreamSynchronize(stream));
   // every rank's arena is zeroed and mapped before anyone may launch
@@ -484,6 +492,7 @@ cudaError_t MoeKernelLauncher::DebugRead(int which, void* dst, size_t offset, si
     case 7:
       memcpy(dst, info, std::min(bytes, sizeof(info)));
       return cudaSuccess;
+    case 8: src = prof_; size = prof_ ? (size_t)grid_ * FDMOE_PROF_EVENTS * 16 : 0; break;
     default: return cudaErrorInvalidValue;
   }
   if (offset >= size) return cudaSuccess;

@@ -56,6 +56,7 @@ struct __align__(16) SmemCtl {
   int32_t flag;
   uint32_t q_t0;
   uint32_t q_total;
+  uint32_t prof_n;
   uint32_t cnt[128];
   uint32_t base[128];
   uint32_t pre[132];
@@ -153,6 +154,19 @@ __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Optional event trace (one writer thread per phase): {kind, t0, t1, t2} in ns,
+// low 32 bits of the global timer.  Slot 0 of each CTA holds the event count.
+__device__ __forceinline__ uint32_t prof_now() { return (uint32_t)ptx::globaltimer_ns(); }
+__device__ __forceinline__ void prof_event(const FdmoeParams& p, SmemCtl& sc, uint32_t kind,
+                                           uint32_t t0, uint32_t t1, uint32_t t2) {
+  if (!p.prof) return;
+  const uint32_t i = ++sc.prof_n;
+  if (i >= FDMOE_PROF_EVENTS) return;
+  uint32_t* e = p.prof + ((size_t)blockIdx.x * FDMOE_PROF_EVENTS + i) * 4;
+  e[0] = kind; e[1] = t0; e[2] = t1; e[3] = t2;
+  p.prof[(size_t)blockIdx.x * FDMOE_PROF_EVENTS * 4] = i;
 }
 
 // ------------------------------------------------------- error / abort path
@@ -303,6 +317,7 @@ __device__ void gate_tile(const FdmoeParams& p, uint8_t* stage, SmemCtl& sc, int
   const FdmoePeer& me = p.peers[p.rank];
 
   if (tid < 128) sc.cnt[tid] = 0;
+  const uint32_t pt0 = p.prof ? prof_now() : 0u;
 
   // ---- gate GEMM: warps 0-3 compute (8 tokens x 4 experts per thread), warps
   // 4-11 stage the next 32-wide k chunk (bf16 -> fp32, transposed to [k][row]).
@@ -387,6 +402,7 @@ __device__ void gate_tile(const FdmoeParams& p, uint8_t* stage, SmemCtl& sc, int
           make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
   }
   __syncthreads();
+  const uint32_t pt1 = p.prof ? prof_now() : 0u;
 
   // ---- top-k + softmax: one warp per token, 4 logits per lane.
   for (int tok = warp; tok < nt; tok += kThreads / 32) {
@@ -479,12 +495,10 @@ __device__ void gate_tile(const FdmoeParams& p, uint8_t* stage, SmemCtl& sc, int
             if (vi < H / 8) dst[vi] = r[i];
           }
           if (seg == 0 && lane == 0) {
-            FdmoeRowMeta m;
-            m.token = t0 + tok;
-            m.home_slot = (p.rank << 8) | k;
-            m.weight = sc.tk_w[tok][k];
-            m.pad = 0;
-            *reinterpret_cast<uint4*>(&p.peers[owner].meta[row]) = *reinterpret_cast<uint4*>(&m);
+            // FdmoeRowMeta {token, home << 8 | slot, weight, pad} as one 16-byte store
+            *reinterpret_cast<uint4*>(&p.peers[owner].meta[row]) =
+                make_uint4((uint32_t)(t0 + tok), (uint32_t)((p.rank << 8) | k),
+                           __float_as_uint(sc.tk_w[tok][k]), 0u);
           }
         }
       }
@@ -517,6 +531,7 @@ __device__ void gate_tile(const FdmoeParams& p, uint8_t* stage, SmemCtl& sc, int
   }
   __syncthreads();
   if (tid == 0) {
+    prof_event(p, sc, 100u, pt0, pt1, prof_now());
     fence_acqrel<S>();
     const uint32_t done = atomicAdd(&me.ctl->gate_done, 1u) + 1u;
     if (done == (uint32_t)n_tiles) gate_phase_finished<S>(p);
@@ -716,6 +731,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
     }
     sc.abort = 0;
     sc.flag = 0;
+    sc.prof_n = 0;
     ptx::fence_mbar_init();
     st_relaxed<S>(&ctl->tokens_launch, (uint32_t)p.T);
   }
@@ -883,10 +899,13 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       const uint32_t kind = t.a & 0xffu;
       if (kind == FDMOE_TASK_EXIT) break;
       const uint32_t e = (t.a >> 8) & 0xfffu, n = t.a >> 20, j = t.b, rows = t.c;
+      const uint32_t pt0 = (p.prof && etid == 0) ? prof_now() : 0u;
+      uint32_t pt1 = pt0;
       if (kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2) {
         const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
         ++tile_it;
         if (!epi_vote_all(wait_bar(p, sc, &sc.tmem_full[acc], aph, FDMOE_ERR_TIMEOUT_TMEM))) break;
+        if (p.prof && etid == 0) pt1 = prof_now();
         ptx::tcgen05_fence_after();
         const uint32_t taddr = tmem_base + acc * kAccCols;
         if (kind == FDMOE_TASK_FFN1)
@@ -992,6 +1011,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           if (done == p.expected_static) st_release<false>(&ctl->closed, 1u);
         }
       }
+      if (etid == 0) prof_event(p, sc, kind, pt0, pt1, prof_now());
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&sc.ring_empty[r]);
     }

@@ -140,7 +140,10 @@ typedef struct {
   uint32_t* ffn2_done;  // [El * MT]
   uint32_t* status_host;  // mapped pinned word: first error code, readable without a sync
   int32_t* test_buf;    // task-system self test payload
+  uint32_t* prof;       // optional event trace, FDMOE_PROF_EVENTS x 4 words per CTA (NULL = off)
 } FdmoeParams;
+
+enum { FDMOE_PROF_EVENTS = 512 };
 
 // Thin C ABI between the C++ host launcher and the CUDA translation unit.
 // All functions return a cudaError_t value as int.

@@ -61,7 +61,9 @@ int FlashMoeGetLastStatus(FlashMoeHandle h, uint32_t* code, uint32_t* info);
  * `which`: 0 top-k indices int32 [T,K]; 1 routing weights fp32 [T,K];
  * 2 rows per local expert uint32 [E_local]; 3 packed rows bf16 [E_local*cap,H];
  * 4 row sideband 16 B [E_local*cap]; 5 activations bf16 [E_local*cap,I];
- * 6 weighted expert outputs bf16 [maxTokens,K,H]; 7 {cap_rows, E_local, grid, smem} int32[4].
+ * 6 weighted expert outputs bf16 [maxTokens,K,H]; 7 {cap_rows, E_local, grid, smem} int32[4];
+ * 8 event trace of the last launch (only with FLASHMOE_PROFILE=1 at create): per CTA 512 records of
+ * {kind, t0, t1, t2} uint32 ns, record 0 = {count,...}.
  * Copies min(bytes, size) bytes starting at `offset` to host memory `dst`
  * after synchronising the device. */
 int FlashMoeDebugRead(FlashMoeHandle h, int which, void* dst, size_t offset, size_t bytes);

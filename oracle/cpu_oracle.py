@@ -29,7 +29,9 @@ _i32p = np.ctypeslib.ndpointer(dtype=np.int32, flags="C_CONTIGUOUS")
 
 def build(ref_root: str = "/root/reference") -> None:
     """Compile the port, and the reference library when its sources are present."""
-    subprocess.run(["make", "-s", "-C", _HERE, f"REF={ref_root}", "oracle", "ref"], check=True)
+    # quiet on stdout: callers such as the benchmark print exactly one JSON line there
+    subprocess.run(["make", "-s", "-C", _HERE, f"REF={ref_root}", "oracle", "ref"], check=True,
+                   stdout=subprocess.DEVNULL)
 
 
 def _ptr(a: Optional[np.ndarray], ty=C.c_float):

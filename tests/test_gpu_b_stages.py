@@ -1,0 +1,97 @@
+"""GPU parity, stage by stage, from one full launch per case: gate (top-k indices exact, weights),
+routing/pack (row counts, sideband, payload), FFN1 activations, FFN2 weighted rows, final output.
+
+Twins of the reference's stage tests (test/singleGPU/cpp/moe/internal/moeGateTest.hip:62-109,
+moeRoutingTest.hip:286-353, moeExpertFFN1Test.hip:58-106, moeExpertsTests.hip:389-475) and of its
+integration test (test/singleGPU/cpp/moe/moeTest.cpp:28-70).  Everything is checked against the CPU
+oracle on the same bf16-rounded inputs; bf16 tolerances are the north-star ones (max-abs 2e-2,
+rel-L2 1e-2)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import moe_testlib as tl
+from moe_testlib import cpu_oracle, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def check_layer(shape, x, gate, w13, w2, max_tokens, golden=None, inplace=False, check_stages=True):
+    port = cpu_oracle.PortOracle()
+    T = x.shape[0]
+    K, H, I = shape.topk, shape.hidden, shape.inter
+    xf, gf, w13f, w2f = tl.f32(x), tl.f32(gate), tl.f32(w13), tl.f32(w2)
+    o_out, o_w, o_idx, o_act, o_y = port.full_moe(xf, gf, w13f, w2f, K, threads=port.max_threads(), stages=True)
+    if golden is not None:
+        g = np.load(os.path.join(tl.GOLDEN, golden))
+        assert np.array_equal(o_idx, g["topk_idx"]) and np.array_equal(o_out, g["out"])
+
+    layer = tl.GpuLayer(shape, gate, w13, w2, max_tokens)
+    try:
+        out = tl.f32(layer.run(x, inplace=inplace))
+        st = layer.stages(T) if check_stages else None
+    finally:
+        layer.close()
+
+    if check_stages:
+        # --- gate: indices bit-exact (the gate GEMM reproduces the reference's fp32 order), weights to 1e-6
+        assert np.array_equal(st["idx"], o_idx), f"top-k mismatch on {(st['idx'] != o_idx).any(1).sum()} tokens"
+        assert np.abs(st["w"] - o_w).max() <= 1e-6
+        # --- routing: per-expert row counts and the (token, slot) set of each expert
+        cap = layer.cap_rows
+        for e in range(shape.experts):
+            want = {(t, k) for t, k in zip(*np.nonzero(o_idx == e))}
+            assert st["cnt"][e] == len(want), f"expert {e}: {st['cnt'][e]} rows, expected {len(want)}"
+            m = st["meta"][e * cap:e * cap + len(want)]
+            got = {(int(t), int(hs) & 0xff) for t, hs in zip(m[:, 0], m[:, 1])}
+            assert got == want, f"expert {e}: wrong (token, slot) set"
+        # --- per-row checks on every packed row
+        act_got, act_ref = [], []
+        for e in range(shape.experts):
+            n = int(st["cnt"][e])
+            if n == 0:
+                continue
+            m = st["meta"][e * cap:e * cap + n]
+            toks, slots = m[:, 0], m[:, 1] & 0xff
+            wts = m[:, 2].copy().view(np.float32)
+            assert torch.equal(st["packed"][e * cap:e * cap + n], x[torch.from_numpy(toks.astype(np.int64))])
+            assert np.abs(wts - o_w[toks, slots]).max() <= 1e-6
+            act_got.append(tl.f32(st["act"][e * cap:e * cap + n]))
+            act_ref.append(o_act[toks, slots])
+        tl.assert_close_bf16(np.concatenate(act_got), np.concatenate(act_ref), "FFN1 activations")
+        tl.assert_close_bf16(tl.f32(st["y"]), o_y * o_w[:, :, None], "FFN2 weighted rows")
+
+    assert np.isfinite(out).all()
+    tl.assert_close_bf16(out, o_out, "layer output")
+    max_abs, rl2 = float(np.abs(out - o_out).max()), tl.rel_l2(out, o_out)
+    return max_abs, rl2
+
+
+def test_tiny_layer_ragged_tokens():
+    s = synth.TINY
+    gate, w13, w2 = synth.make_weights(s, seed=0, std=0.05)
+    check_layer(s, synth.make_tokens(s, 40, seed=0), gate, w13, w2, max_tokens=48, golden="tiny_t40.npz")
+
+
+def test_tiny_layer_many_tiles_per_expert():
+    # 1000 tokens x 4 slots over 32 experts: about 125 rows per expert, some experts cross a 128-row tile
+    s = synth.TINY
+    gate, w13, w2 = synth.make_weights(s, seed=1, std=0.05)
+    check_layer(s, synth.make_tokens(s, 1000, seed=1), gate, w13, w2, max_tokens=1000)
+
+
+def test_qwen3_30b_first_config_128_tokens():
+    s = synth.QWEN3_30B_A3B
+    gate, w13, w2 = synth.make_weights(s, seed=0)
+    check_layer(s, synth.make_tokens(s, 128, seed=0), gate, w13, w2, max_tokens=128,
+                golden="qwen3_30b_t128_seed0.npz")
+
+
+def test_qwen3_30b_reference_test_stream_48_tokens_in_place():
+    # the reference's own moeTest: 48 tokens of its srand(7907) stream, maxTokens = tokens + 2,
+    # output aliasing the input as its vLLM wrapper does
+    x, gate, w13, w2 = tl.reference_stream_inputs(48)
+    check_layer(synth.QWEN3_30B_A3B, x, gate, w13, w2, max_tokens=50, golden="qwen3_30b_t48_refstream.npz",
+                inplace=True)
