@@ -179,6 +179,7 @@ class MoeKernelLauncher final : public moe::IMoeKernelLauncher {
   void* act_ = nullptr;
   int32_t* topk_idx_ = nullptr;
   float* topk_w_ = nullptr;
+  int32_t* dest_row_ = nullptr;
   uint32_t* status_host_ = nullptr;
   uint32_t* status_dev_ = nullptr;
   // fp32 I/O mode: bf16 copies of the weights and token staging
@@ -187,6 +188,8 @@ class MoeKernelLauncher final : public moe::IMoeKernelLauncher {
   // host-buffer entry point staging
   void *host_in_dev_ = nullptr, *host_out_dev_ = nullptr;
   uint32_t* prof_ = nullptr;  // optional event trace (FLASHMOE_PROFILE=1)
+  float* debug_logits_ = nullptr;  // optional gate-logit dump (FLASHMOE_DEBUG_LOGITS=1)
+  EncodeTiledFn encode_ = nullptr;
   Bootstrap boot_;
   bool inited_ = false;
 };
@@ -195,16 +198,18 @@ void MoeKernelLauncher::FreeAll() {
   for (int r = 0; r < (int)peer_bases_.size(); ++r)
     if (r != rank_ && peer_bases_[r]) cudaIpcCloseMemHandle(peer_bases_[r]);
   peer_bases_.clear();
-  void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, gate_bf16_, w13_bf16_, w2_bf16_,
-                  tok_bf16_, out_bf16_, host_in_dev_, host_out_dev_, prof_};
+  void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, dest_row_, gate_bf16_, w13_bf16_, w2_bf16_,
+                  tok_bf16_, out_bf16_, host_in_dev_, host_out_dev_, prof_, debug_logits_};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   arena_ = nullptr;
   act_ = nullptr;
   topk_idx_ = nullptr;
   topk_w_ = nullptr;
+  dest_row_ = nullptr;
   gate_bf16_ = w13_bf16_ = w2_bf16_ = tok_bf16_ = out_bf16_ = host_in_dev_ = host_out_dev_ = nullptr;
   prof_ = nullptr;
+  debug_logits_ = nullptr;
   if (status_host_) cudaFreeHost(status_host_);
   status_host_ = nullptr;
   boot_.Close();
@@ -308,6 +313,7 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   CUDA_ERROR_CHECK(cudaMalloc(&act_, (size_t)g_.El * g_.cap_rows * g_.I * 2));
   CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&topk_idx_), std::max<size_t>(4, (size_t)maxTokens * g_.K * 4)));
   CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&topk_w_), std::max<size_t>(4, (size_t)maxTokens * g_.K * 4)));
+  CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&dest_row_), std::max<size_t>(4, (size_t)maxTokens * g_.K * 4)));
   CUDA_ERROR_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped));
   memset(status_host_, 0, 64);
   CUDA_ERROR_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_), status_host_, 0));
@@ -367,6 +373,8 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_w13, w13_dev, (uint64_t)g_.El * 2 * g_.I, g_.H, 128));
   CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_act, act_, exp_rows, g_.I, 128));
   CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_w2, w2_dev, (uint64_t)g_.El * g_.H, g_.I, 256));
+  CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_gate, gate_dev, (uint64_t)g_.E, g_.H, std::min(128, g_.E)));
+  encode_ = enc;
   for (int r = 0; r < world; ++r) {
     uint8_t* b = static_cast<uint8_t*>(peer_bases_[r]);
     FdmoePeer& pv = params_.peers[r];
@@ -391,14 +399,20 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   params_.queue_mask = (int32_t)(g_.queue_cap - 1);
   params_.combine_group = g_.combine_group;
   params_.eager = EnvInt("FLASHMOE_EAGER", world > 1 ? 1 : 0);
+  params_.debug_flags = EnvInt("FLASHMOE_DEBUG_FLAGS", 0);
   params_.timeout_ns = (uint64_t)std::max(1, EnvInt("FLASHMOE_TIMEOUT_MS", 2000)) * 1000000ull;
   params_.gate_w = gate_dev;
   params_.act = act_;
   params_.topk_idx = topk_idx_;
   params_.topk_w = topk_w_;
+  params_.dest_row = dest_row_;
   params_.ffn1_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn1_done);
   params_.ffn2_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn2_done);
   params_.status_host = status_dev_;
+  if (EnvInt("FLASHMOE_DEBUG_LOGITS", 0)) {
+    CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&debug_logits_), std::max<size_t>(4, (size_t)maxTokens * 128 * 4)));
+    params_.debug_logits = debug_logits_;
+  }
   if (EnvInt("FLASHMOE_PROFILE", 0)) {
     const size_t bytes = (size_t)grid_ * FDMOE_PROF_EVENTS * 16;
     CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&prof_), bytes));
@@ -435,6 +449,10 @@ cudaError_t MoeKernelLauncher::LaunchBf16(const void* tokens, void* output, int 
   ++epoch_;
   CUDA_ERROR_CHECK(cudaMemsetAsync(arena_ + layout_.zero_begin, 0, layout_.zero_end - layout_.zero_begin, stream));
   FdmoeParams p = params_;
+  if (tokensNum > 0 && mode == 0) {
+    // the token matrix moves between launches: its TMA descriptor is rebuilt (host-only arithmetic)
+    CUDA_ERROR_CHECK(MakeTensorMap(encode_, &p.tm_x, tokens, (uint64_t)tokensNum, g_.H, std::min(128, tokensNum)));
+  }
   p.T = tokensNum;
   p.x = tokens;
   p.out = output;
@@ -492,6 +510,7 @@ cudaError_t MoeKernelLauncher::DebugRead(int which, void* dst, size_t offset, si
     case 7:
       memcpy(dst, info, std::min(bytes, sizeof(info)));
       return cudaSuccess;
+    case 9: src = debug_logits_; size = debug_logits_ ? (size_t)g_.max_tokens_local * 128 * 4 : 0; break;
     case 8: src = prof_; size = prof_ ? (size_t)grid_ * FDMOE_PROF_EVENTS * 16 : 0; break;
     default: return cudaErrorInvalidValue;
   }

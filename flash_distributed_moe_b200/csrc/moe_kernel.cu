@@ -1,12 +1,17 @@
 // The persistent MoE-layer kernel for sm_100a and its thin C ABI.
 //
-// One CTA per SM.  Phase A: CTAs claim 32-token gate tiles (fp32 gate GEMM in
-// the reference's accumulation order, top-k, fp32/fp64 softmax, row pack into
-// the owning rank's expert buffers).  Phase B: every CTA becomes a worker that
-// pulls tile tasks from a ticket-based global queue: FFN1 (SwiGLU) and FFN2
-// (down projection) tiles run on tcgen05 with TMEM accumulators fed by TMA,
-// COMBINE sums a token group's K result rows in slot order.  Cross-GPU traffic
-// is plain stores and scoped atomics into peers' symmetric buffers.
+// One CTA per SM, every CTA a worker that pulls tasks from a ticket-based global
+// queue and overlaps four kinds of work:
+//   GATE    128-token tile: gate GEMM on tcgen05, top-k, fp64 softmax, row
+//           reservation in the owners' expert buffers (tokens whose leading
+//           logits are nearly tied are recomputed with fp32 FMAs in the
+//           reference's accumulation order, so the selection is the reference's);
+//   PACK    16-token group: copies the token rows to their K destinations;
+//   FFN1/2  128-row expert tiles on tcgen05 with TMEM accumulators fed by TMA
+//           (SwiGLU epilogue; routing-weight epilogue stored on the home rank);
+//   COMBINE token group: ordered sum of the K weighted rows.
+// Cross-GPU traffic is plain stores and scoped atomics into peers' symmetric
+// buffers.
 //
 // Counterparts in the reference project (HIP, MI300X):
 //   persistent kernel + phases     src/hip/kernel/moeKernel.h:37-107
@@ -17,6 +22,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
+#include <stddef.h>
 #include <stdint.h>
 
 #include "moe_types.h"
@@ -52,22 +58,43 @@ struct __align__(16) SmemCtl {
   FdmoeSlot ring[kRing];
   uint32_t tmem_base;
   volatile uint32_t abort;
-  int32_t cur_tile;
   int32_t flag;
   uint32_t q_t0;
   uint32_t q_total;
   uint32_t prof_n;
-  uint32_t cnt[128];
-  uint32_t base[128];
+  uint32_t n_flagged;
+  // flush scratch (per local expert)
   uint32_t pre[132];
   uint32_t full_tiles[128];
   uint32_t rem_rows[128];
-  int32_t tk_idx[FDMOE_GATE_TOKENS][FDMOE_MAX_TOPK];
-  float tk_w[FDMOE_GATE_TOKENS][FDMOE_MAX_TOPK];
-  uint32_t lpos[FDMOE_GATE_TOKENS][FDMOE_MAX_TOPK];
+  // The epilogue group runs one task at a time, so the scratch of a GATE task
+  // and the store staging of an FFN task share storage.  16-byte aligned: the
+  // staging buffer is accessed with 16-byte vector loads and stores.
+  union alignas(16) {
+    struct {
+      // gate-tile scratch (per expert / per token of the tile)
+      uint32_t cnt[128];
+      uint32_t base[128];
+      uint32_t flagged[FDMOE_GATE_TOKENS];
+      float exact[8][128];                      // exact logits of the tokens being recomputed
+      float half_v[2][FDMOE_GATE_TOKENS][9];    // top-9 of each 64-column half
+      uint8_t half_i[2][FDMOE_GATE_TOKENS][12];
+      float top_v[FDMOE_GATE_TOKENS][9];        // merged top-9 logits, descending
+      uint8_t top_i[FDMOE_GATE_TOKENS][12];
+      float tk_w[FDMOE_GATE_TOKENS][FDMOE_MAX_TOPK];
+      uint8_t lpos[FDMOE_GATE_TOKENS][FDMOE_MAX_TOPK];
+    };
+    // FFN epilogues: per-warp staging of a 32-row x 64-byte chunk (80-byte pitch
+    // keeps the 16-byte accesses of a quarter warp on distinct banks)
+    uint8_t store_stage[kEpiThreads / 32][32 * 80];
+  };
 };
 
 constexpr int kSmemBytes = kStages * kStageBytes + (int)sizeof(SmemCtl) + 1024;
+static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA exceeds the sm_100 limit");
+static_assert(offsetof(SmemCtl, store_stage) % 16 == 0 && (32 * 80) % 16 == 0 && 80 % 16 == 0,
+              "store staging must keep 16-byte alignment for every warp and row");
+static_assert(offsetof(SmemCtl, full_bar) % 8 == 0 && offsetof(SmemCtl, ring) % 16 == 0, "barrier / ring alignment");
 
 // ------------------------------------------------------------ scoped helpers
 template <bool S>
@@ -167,6 +194,11 @@ __device__ __forceinline__ void prof_event(const FdmoeParams& p, SmemCtl& sc, ui
   uint32_t* e = p.prof + ((size_t)blockIdx.x * FDMOE_PROF_EVENTS + i) * 4;
   e[0] = kind; e[1] = t0; e[2] = t1; e[3] = t2;
   p.prof[(size_t)blockIdx.x * FDMOE_PROF_EVENTS * 4] = i;
+}
+
+// Single timestamp mark (trace builds of the analysis only; one writer thread).
+__device__ __forceinline__ void prof_mark(const FdmoeParams& p, SmemCtl& sc, int etid, uint32_t id) {
+  if (p.prof && etid == 0) prof_event(p, sc, 200u + id, prof_now(), 0u, 0u);
 }
 
 // ------------------------------------------------------- error / abort path
@@ -272,16 +304,10 @@ __device__ __forceinline__ void maybe_close(const FdmoeParams& p) {
   st_release<false>(&ctl->closed, 1u);
 }
 
-// This rank's gate phase is complete (all its rows are written and fenced):
+// Every token of this rank is packed (all its rows are written and fenced):
 // tell every rank; whoever completes a rank's count asks it to flush.
 template <bool S>
 __device__ void gate_phase_finished(const FdmoeParams& p) {
-  FdmoeCtl* ctl = p.peers[p.rank].ctl;
-  if (p.mode == 1) {
-    fence_acqrel<false>();
-    st_release<false>(&ctl->closed, 1u);
-    return;
-  }
   for (int q = 0; q < p.world; ++q) {
     fence_acqrel<S>();
     const uint32_t prev = atom_add<S>(&p.peers[q].ctl->ranks_done, 1u);
@@ -296,255 +322,384 @@ __device__ void gate_phase_finished(const FdmoeParams& p) {
   }
 }
 
-// ================================================================== phase A
-// One gate tile: logits for 32 tokens x E experts with fp32 FMAs, k strictly
-// ascending per output (bf16 x bf16 products are exact in fp32, so this equals
-// the reference's `acc += a*b` bit for bit), top-k with the lower index winning
-// ties, softmax over the kept logits in double, then the rows are packed into
-// the owners' expert buffers.
-template <bool S>
-__device__ void gate_tile(const FdmoeParams& p, uint8_t* stage, SmemCtl& sc, int tile,
-                          int n_tiles) {
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int H = p.H, E = p.E, K = p.K;
-  const int t0 = tile * FDMOE_GATE_TOKENS;
-  const int nt = min(FDMOE_GATE_TOKENS, p.T - t0);
-  float* As = reinterpret_cast<float*>(stage);  // [2][32 k][32 tok]
-  float* Bs = As + 2 * 32 * 32;                 // [2][32 k][128 exp]
-  float* logits = Bs + 2 * 32 * 128;            // [32 tok][128 exp]
-  const bf16* x = reinterpret_cast<const bf16*>(p.x);
-  const bf16* wg = reinterpret_cast<const bf16*>(p.gate_w);
-  const FdmoePeer& me = p.peers[p.rank];
-
-  if (tid < 128) sc.cnt[tid] = 0;
-  const uint32_t pt0 = p.prof ? prof_now() : 0u;
-
-  // ---- gate GEMM: warps 0-3 compute (8 tokens x 4 experts per thread), warps
-  // 4-11 stage the next 32-wide k chunk (bf16 -> fp32, transposed to [k][row]).
-  float acc[8][4];
+// ===================================================================== GATE
+// Top-9 of the 64 logits one thread holds (columns c0..c0+63 of its token row,
+// as two raw 32-word TMEM loads), descending, the lower column winning ties.
+// Branch-free selection rounds; a selected entry is replaced by -inf.
+__device__ __forceinline__ void top9_of_64(uint32_t (&lo)[32], uint32_t (&hi)[32], int c0, int E, float (&tv)[9],
+                                           int (&ti)[9]) {
+  const uint32_t ninf = 0xff800000u;
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-
-  const int nchunks = H / 32;
-  auto stage_chunk = [&](int c, int b) {
-    uint4 v[3];
-    int pidx[3];
-#pragma unroll
-    for (int u = 0; u < 3; ++u) {
-      const int pi = (tid - 128) + u * 256;
-      pidx[u] = pi;
-      v[u] = make_uint4(0, 0, 0, 0);
-      if (pi < 128) {
-        const int r = pi & 31, q = pi >> 5;
-        if (r < nt) v[u] = *reinterpret_cast<const uint4*>(x + (size_t)(t0 + r) * H + c * 32 + q * 8);
-      } else if (pi < 640) {
-        const int pp = pi - 128;
-        const int r = pp & 127, q = pp >> 7;
-        if (r < E) v[u] = __ldg(reinterpret_cast<const uint4*>(wg + (size_t)r * H + c * 32 + q * 8));
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < 3; ++u) {
-      const int pi = pidx[u];
-      float* dst;
-      int stride;
-      if (pi < 128) {
-        const int r = pi & 31, q = pi >> 5;
-        dst = As + b * 1024 + (q * 8) * 32 + r;
-        stride = 32;
-      } else if (pi < 640) {
-        const int pp = pi - 128;
-        const int r = pp & 127, q = pp >> 7;
-        dst = Bs + b * 4096 + (q * 8) * 128 + r;
-        stride = 128;
-      } else {
-        continue;
-      }
-      const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        dst[(2 * i) * stride] = bf16_lo(w[i]);
-        dst[(2 * i + 1) * stride] = bf16_hi(w[i]);
-      }
-    }
-  };
-
-  if (tid >= 128) stage_chunk(0, 0);
-  __syncthreads();
-  for (int c = 0; c < nchunks; ++c) {
-    const int b = c & 1;
-    if (tid >= 128) {
-      if (c + 1 < nchunks) stage_chunk(c + 1, b ^ 1);
-    } else {
-      const float* a = As + b * 1024 + warp * 8;
-      const float* bb = Bs + b * 4096 + lane * 4;
-#pragma unroll 8
-      for (int k = 0; k < 32; ++k) {
-        const float4 a0 = *reinterpret_cast<const float4*>(a + k * 32);
-        const float4 a1 = *reinterpret_cast<const float4*>(a + k * 32 + 4);
-        const float4 bv = *reinterpret_cast<const float4*>(bb + k * 128);
-        const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-        const float bw[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bw[j], acc[i][j]);
-      }
-    }
-    __syncthreads();
+  for (int c = 0; c < 32; ++c) {
+    if (c0 + c >= E) lo[c] = ninf;
+    if (c0 + 32 + c >= E) hi[c] = ninf;
   }
-  if (tid < 128) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-      *reinterpret_cast<float4*>(logits + (warp * 8 + i) * 128 + lane * 4) =
-          make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-  }
-  __syncthreads();
-  const uint32_t pt1 = p.prof ? prof_now() : 0u;
-
-  // ---- top-k + softmax: one warp per token, 4 logits per lane.
-  for (int tok = warp; tok < nt; tok += kThreads / 32) {
-    float v[4];
-    uint32_t taken = 0;
+  for (int r = 0; r < 9; ++r) {
+    float b0 = -INFINITY, b1 = -INFINITY;
+    int i0 = 255, i1 = 255;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int e = lane + 32 * i;
-      v[i] = (e < E) ? logits[tok * 128 + e] : -INFINITY;
-      if (e >= E) taken |= 1u << i;
+    for (int c = 0; c < 32; ++c) {
+      const float f0 = __uint_as_float(lo[c]), f1 = __uint_as_float(hi[c]);
+      const bool g0 = f0 > b0;
+      b0 = g0 ? f0 : b0;
+      i0 = g0 ? c : i0;
+      const bool g1 = f1 > b1;
+      b1 = g1 ? f1 : b1;
+      i1 = g1 ? 32 + c : i1;
     }
-    float myv = 0.f;
-    int myi = 0;
-    for (int k = 0; k < K; ++k) {
-      float bv = -INFINITY;
-      int bi = 0x7fffffff;
+    const bool up = b1 > b0;  // the upper chain wins only when strictly greater
+    const float bv = up ? b1 : b0;
+    const int bi = up ? i1 : i0;
+    tv[r] = bv;
+    ti[r] = bi == 255 ? 255 : c0 + bi;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int e = lane + 32 * i;
-        if (!((taken >> i) & 1u) && (v[i] > bv || (v[i] == bv && e < bi))) {
-          bv = v[i];
-          bi = e;
-        }
-      }
-#pragma unroll
-      for (int off = 16; off >= 1; off >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-        if (ov > bv || (ov == bv && oi < bi)) {
-          bv = ov;
-          bi = oi;
-        }
-      }
-      if ((bi & 31) == lane && bi < 128) taken |= 1u << (bi >> 5);
-      if (lane == k) {
-        myv = bv;
-        myi = bi;
-      }
+    for (int c = 0; c < 32; ++c) {
+      if (c == bi) lo[c] = ninf;
+      if (32 + c == bi) hi[c] = ninf;
     }
-    // softmax over the K kept logits: running-max form of the reference with the
-    // values already in descending order, so the max is the first one and the
-    // sum is accumulated as 1 + e_1 + e_2 + ... in that order, all in double.
-    const double m = (double)__shfl_sync(0xffffffffu, myv, 0);
-    const double ex = (lane < K) ? exp((double)myv - m) : 0.0;
-    double sum = 1.0;
-    for (int j = 1; j < K; ++j) sum += __shfl_sync(0xffffffffu, ex, j);
-    const float w = (float)(ex / sum);
-    if (lane < K) {
-      p.topk_idx[(size_t)(t0 + tok) * K + lane] = myi;
-      p.topk_w[(size_t)(t0 + tok) * K + lane] = w;
-      sc.tk_idx[tok][lane] = myi;
-      sc.tk_w[tok][lane] = w;
-      sc.lpos[tok][lane] = atomicAdd(&sc.cnt[myi & 127], 1u);
-    }
-  }
-  __syncthreads();
-
-  // ---- reserve rows in the owners' expert buffers: one atomic per expert.
-  if (tid < E) {
-    const uint32_t cnt = sc.cnt[tid];
-    if (cnt) {
-      const int owner = tid / p.El, le = tid - owner * p.El;
-      const uint32_t base = atom_add<S>(&p.peers[owner].expert_cnt[le], cnt);
-      if (base + cnt > (uint32_t)p.cap_rows) raise_error(p, sc, FDMOE_ERR_ROW_OVERFLOW, tid);
-      sc.base[tid] = base;
-    }
-  }
-  __syncthreads();
-
-  // ---- pack: copy each token row to its K destinations, one warp per token.
-  if (!sc.abort) {
-    for (int tok = warp; tok < nt; tok += kThreads / 32) {
-      const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(t0 + tok) * H);
-      for (int seg = 0; seg < H / 2048 + ((H % 2048) ? 1 : 0); ++seg) {
-        uint4 r[8];
-        const int vbase = seg * 256;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int vi = vbase + lane + 32 * i;
-          r[i] = (vi < H / 8) ? src[vi] : make_uint4(0, 0, 0, 0);
-        }
-        for (int k = 0; k < K; ++k) {
-          const int e = sc.tk_idx[tok][k];
-          const int owner = e / p.El, le = e - owner * p.El;
-          const size_t row = (size_t)le * p.cap_rows + sc.base[e] + sc.lpos[tok][k];
-          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.peers[owner].packed) + row * H);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int vi = vbase + lane + 32 * i;
-            if (vi < H / 8) dst[vi] = r[i];
-          }
-          if (seg == 0 && lane == 0) {
-            // FdmoeRowMeta {token, home << 8 | slot, weight, pad} as one 16-byte store
-            *reinterpret_cast<uint4*>(&p.peers[owner].meta[row]) =
-                make_uint4((uint32_t)(t0 + tok), (uint32_t)((p.rank << 8) | k),
-                           __float_as_uint(sc.tk_w[tok][k]), 0u);
-          }
-        }
-      }
-    }
-  }
-  ptx::fence_proxy_async();  // packed rows are read by TMA later
-  __syncthreads();
-
-  // ---- landed accounting (eager mode): the writer that completes a 128-row
-  // tile publishes its FFN1 tasks on the owner's queue.
-  if (p.eager && p.mode == 0 && tid < E && sc.cnt[tid]) {
-    const uint32_t cnt = sc.cnt[tid], base = sc.base[tid];
-    const int owner = tid / p.El, le = tid - owner * p.El;
-    const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
-    fence_acqrel<S>();
-    const uint32_t j0 = base / 128u, j1 = (base + cnt - 1u) / 128u;
-    for (uint32_t j = j0; j <= j1; ++j) {
-      const uint32_t lo = max(base, j * 128u), hi = min(base + cnt, (j + 1u) * 128u);
-      const uint32_t add = hi - lo;
-      const uint32_t prev = atom_add<S>(&p.peers[owner].tile_landed[(size_t)le * p.MT + j], add);
-      if (prev + add == 128u) {
-        fence_acqrel<S>();
-        queue_push<S>(p, p.peers[owner], nt1, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
-          a = task_word(FDMOE_TASK_FFN1, (uint32_t)le, i);
-          b = j;
-          c = 128u;
-        });
-      }
-    }
-  }
-  __syncthreads();
-  if (tid == 0) {
-    prof_event(p, sc, 100u, pt0, pt1, prof_now());
-    fence_acqrel<S>();
-    const uint32_t done = atomicAdd(&me.ctl->gate_done, 1u) + 1u;
-    if (done == (uint32_t)n_tiles) gate_phase_finished<S>(p);
   }
 }
 
-// ================================================================== phase B
+// Exact gate logits of up to four tokens for one expert: fp32 FMAs with k
+// strictly ascending per output (bf16 x bf16 products are exact in fp32, so this
+// equals the reference's `acc += a*b` bit for bit; reference refGemm.h:16-27).
+// The four accumulation chains are independent, which hides the FMA latency;
+// the weight row is prefetched 64 elements ahead.
+__device__ __forceinline__ void exact_logits4(const FdmoeParams& p, const int (&tok)[4], int e, float (&acc)[4]) {
+  const int H = p.H;
+  const uint4* w = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.gate_w) + (size_t)e * H);
+  const uint4* x[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    x[i] = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.x) + (size_t)tok[i] * H);
+    acc[i] = 0.f;
+  }
+  uint4 wc[8], wn[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) wc[u] = __ldg(w + u);
+  const int nblk = H / 64;
+  for (int blk = 0; blk < nblk; ++blk) {
+    if (blk + 1 < nblk) {
+#pragma unroll
+      for (int u = 0; u < 8; ++u) wn[u] = __ldg(w + (blk + 1) * 8 + u);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const uint32_t ww[4] = {wc[u].x, wc[u].y, wc[u].z, wc[u].w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 xv = x[i][blk * 8 + u];
+        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[i] = fmaf(bf16_lo(xw[j]), bf16_lo(ww[j]), acc[i]);
+          acc[i] = fmaf(bf16_hi(xw[j]), bf16_hi(ww[j]), acc[i]);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) wc[u] = wn[u];
+  }
+}
+
+// Warp-wide top-k over 128 logits in shared memory (lane l owns experts l,
+// l+32, l+64, l+96), descending, the lower index winning ties (reference
+// refTopk.h:36-58).  Result: lane k < K holds slot k.
+__device__ __forceinline__ void topk_warp(const float* logits, int E, int K, int lane, float& myv, int& myi) {
+  float v[4];
+  uint32_t taken = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = (e < E) ? logits[e] : -INFINITY;
+    if (e >= E) taken |= 1u << i;
+  }
+  myv = 0.f;
+  myi = 0;
+  for (int k = 0; k < K; ++k) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = lane + 32 * i;
+      if (!((taken >> i) & 1u) && (v[i] > bv || (v[i] == bv && e < bi))) {
+        bv = v[i];
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if ((bi & 31) == lane && bi < 128) taken |= 1u << (bi >> 5);
+    if (lane == k) {
+      myv = bv;
+      myi = bi;
+    }
+  }
+}
+
+// Epilogue of a GATE task (256 threads).  The accumulator holds the logits of
+// 128 tokens (TMEM lanes) x 128 experts (columns) as computed by the tensor
+// cores, whose accumulation order is not the reference's.  A token whose
+// leading nine logits contain an adjacent pair closer than `tau` (2.5e-4 of the
+// logit scale, an order of magnitude above the rounding noise of either
+// accumulation order over a few thousand terms) is recomputed exactly; for all
+// other tokens both orders select the same experts in the same order.
+template <bool S>
+__device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, uint64_t* tmem_empty_bar,
+                              int q, int h, int lane, int etid, int ewarp, uint32_t tile) {
+  const int E = p.E, K = p.K;
+  const int t0 = (int)tile * FDMOE_GATE_TOKENS;
+  const int nt = min(FDMOE_GATE_TOKENS, p.T - t0);
+  const int row = q * 32 + lane;
+
+  if (etid < 128) sc.cnt[etid] = 0;
+  if (etid == 0) sc.n_flagged = 0;
+  {
+    uint32_t vlo[32], vhi[32];
+    const uint32_t tb = taddr + ((uint32_t)(q * 32) << 16) + h * 64;
+    ptx::tmem_ld_32x32(tb, vlo);
+    ptx::tmem_ld_32x32(tb + 32, vhi);
+    ptx::tmem_ld_wait();
+    ptx::tcgen05_fence_before();
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(tmem_empty_bar);  // accumulator is free again
+    if (p.debug_logits && row < nt) {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        p.debug_logits[(size_t)(t0 + row) * 128 + h * 64 + c] = __uint_as_float(vlo[c]);
+        p.debug_logits[(size_t)(t0 + row) * 128 + h * 64 + 32 + c] = __uint_as_float(vhi[c]);
+      }
+    }
+    prof_mark(p, sc, etid, 1);
+    float tv[9];
+    int ti[9];
+    top9_of_64(vlo, vhi, h * 64, E, tv, ti);
+    prof_mark(p, sc, etid, 2);
+#pragma unroll
+    for (int j = 0; j < 9; ++j) {
+      sc.half_v[h][row][j] = tv[j];
+      sc.half_i[h][row][j] = (uint8_t)ti[j];
+    }
+  }
+  epi_bar();
+  {
+    // merge by rank: position = own rank + number of partner entries ahead of it;
+    // the lower half (lower expert indices) wins ties
+    const int o = h ^ 1;
+#pragma unroll
+    for (int j = 0; j < 9; ++j) {
+      const float mv = sc.half_v[h][row][j];
+      int pos = j;
+#pragma unroll
+      for (int m = 0; m < 9; ++m) {
+        const float ov = sc.half_v[o][row][m];
+        pos += (h == 0) ? (ov > mv) : (ov >= mv);
+      }
+      if (pos < 9 && mv > -INFINITY) {
+        sc.top_v[row][pos] = mv;
+        sc.top_i[row][pos] = sc.half_i[h][row][j];
+      }
+    }
+  }
+  epi_bar();
+  if (etid < nt) {
+    // etid == row for the first four epilogue warps
+    const int cand = min(E, 9);
+    const float tau = 2.5e-4f * fmaxf(1.0f, fabsf(sc.top_v[etid][0]));
+    bool tie = false;
+    for (int j = 0; j + 1 < cand; ++j) tie |= (sc.top_v[etid][j] - sc.top_v[etid][j + 1]) < tau;
+    if (tie) sc.flagged[atomicAdd(&sc.n_flagged, 1u)] = (uint32_t)etid;
+  }
+  epi_bar();
+  prof_mark(p, sc, etid, 3);
+  // exact recompute of the flagged tokens, eight per pass: each half of the
+  // group takes four tokens, one expert per thread; then one warp per token selects
+  {
+    const uint32_t nf = sc.n_flagged;
+    const int half = etid >> 7, e = etid & 127;
+    for (uint32_t f0 = 0; f0 < nf; f0 += 8) {
+      int tok[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t f = f0 + (uint32_t)(half * 4 + i);
+        tok[i] = t0 + (int)sc.flagged[f < nf ? f : f0];  // out-of-range entries repeat a valid token
+      }
+      if (f0 + (uint32_t)(half * 4) < nf && e < E) {
+        float acc[4];
+        exact_logits4(p, tok, e, acc);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sc.exact[half * 4 + i][e] = acc[i];
+      }
+      epi_bar();
+      if (f0 + (uint32_t)ewarp < nf) {
+        const int tk = (int)sc.flagged[f0 + ewarp];
+        float myv;
+        int myi;
+        topk_warp(sc.exact[ewarp], E, K, lane, myv, myi);
+        if (lane < K) {
+          sc.top_v[tk][lane] = myv;
+          sc.top_i[tk][lane] = (uint8_t)myi;
+        }
+      }
+      epi_bar();
+    }
+  }
+  prof_mark(p, sc, etid, 4);
+  if (etid < nt) {
+    // softmax over the K kept logits, in double, in the reference's order: the
+    // values are descending, so the running max is the first one and the sum is
+    // 1 + e_1 + e_2 + ... (reference refSoftmax.h:23-50)
+    const double m = (double)sc.top_v[etid][0];
+    double ex[FDMOE_MAX_TOPK];
+    double sum = 1.0;
+#pragma unroll
+    for (int k = 0; k < FDMOE_MAX_TOPK; ++k) {
+      if (k < K) {
+        ex[k] = exp((double)sc.top_v[etid][k] - m);
+        if (k > 0) sum += ex[k];
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < FDMOE_MAX_TOPK; ++k) {
+      if (k < K) {
+        const int e = sc.top_i[etid][k];
+        const float w = (float)(ex[k] / sum);
+        sc.tk_w[etid][k] = w;
+        sc.lpos[etid][k] = (uint8_t)atomicAdd(&sc.cnt[e], 1u);
+        p.topk_idx[(size_t)(t0 + etid) * K + k] = e;
+        p.topk_w[(size_t)(t0 + etid) * K + k] = w;
+      }
+    }
+  }
+  epi_bar();
+  prof_mark(p, sc, etid, 5);
+  // reserve rows in the owners' expert buffers: one atomic per expert and tile
+  if (etid < E) {
+    const uint32_t cnt = sc.cnt[etid];
+    if (cnt) {
+      const int owner = etid / p.El, le = etid - owner * p.El;
+      const uint32_t base = atom_add<S>(&p.peers[owner].expert_cnt[le], cnt);
+      if (base + cnt > (uint32_t)p.cap_rows) raise_error(p, sc, FDMOE_ERR_ROW_OVERFLOW, etid);
+      sc.base[etid] = base;
+    }
+  }
+  epi_bar();
+  prof_mark(p, sc, etid, 6);
+  if (etid < nt && !sc.abort) {
+    for (int k = 0; k < K; ++k) {
+      const int e = sc.top_i[etid][k];
+      const int owner = e / p.El, le = e - owner * p.El;
+      const size_t rowg = (size_t)le * p.cap_rows + sc.base[e] + sc.lpos[etid][k];
+      p.dest_row[(size_t)(t0 + etid) * K + k] = (int32_t)rowg;
+      // FdmoeRowMeta {token, home << 8 | slot, weight, pad} as one 16-byte store
+      *reinterpret_cast<uint4*>(&p.peers[owner].meta[rowg]) =
+          make_uint4((uint32_t)(t0 + etid), (uint32_t)((p.rank << 8) | k), __float_as_uint(sc.tk_w[etid][k]), 0u);
+    }
+  }
+  epi_bar();
+  prof_mark(p, sc, etid, 7);
+  if (etid == 0 && !sc.abort) {
+    fence_acqrel<S>();
+    const uint32_t ngroups = (uint32_t)((nt + FDMOE_PACK_TOKENS - 1) / FDMOE_PACK_TOKENS);
+    queue_push<false>(p, p.peers[p.rank], ngroups, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
+      a = FDMOE_TASK_PACK;
+      b = (uint32_t)t0 + i * FDMOE_PACK_TOKENS;
+      c = (uint32_t)min(FDMOE_PACK_TOKENS, nt - (int)i * FDMOE_PACK_TOKENS);
+    });
+  }
+}
+
+// ===================================================================== PACK
+// Copies `count` token rows to their K destinations each (local stores or
+// stores into a peer's expert buffer), one warp per token, then accounts for
+// them.  In eager mode the writer that completes a 128-row tile publishes its
+// FFN1 tasks on the owner's queue.
+template <bool S>
+__device__ __noinline__ void pack_task(const FdmoeParams& p, SmemCtl& sc, int etid, int ewarp, int lane, uint32_t t_first,
+                          uint32_t count) {
+  const int H = p.H, K = p.K;
+  const bf16* x = reinterpret_cast<const bf16*>(p.x);
+  // a warp takes tokens ewarp and ewarp + 8 of the group and keeps the loads of both in flight
+  const bool has[2] = {(uint32_t)ewarp < count, (uint32_t)ewarp + 8u < count};
+  // lane k < K keeps the destination of slot k of both tokens; broadcast by shuffle when needed
+  int my_row[2] = {0, 0}, my_owner[2] = {0, 0};
+  const uint4* src[2];
+#pragma unroll
+  for (int s2 = 0; s2 < 2; ++s2) {
+    const uint32_t t = t_first + (uint32_t)ewarp + 8u * s2;
+    src[s2] = reinterpret_cast<const uint4*>(x + (size_t)(has[s2] ? t : t_first) * H);
+    if (has[s2] && lane < K) {
+      my_row[s2] = __ldcg(&p.dest_row[(size_t)t * K + lane]);
+      my_owner[s2] = __ldcg(&p.topk_idx[(size_t)t * K + lane]) / p.El;
+    }
+  }
+  for (int vbase = 0; vbase < H / 8; vbase += 256) {
+    uint4 r[2][8];
+#pragma unroll
+    for (int s2 = 0; s2 < 2; ++s2) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int vi = vbase + lane + 32 * i;
+        r[s2][i] = (has[s2] && vi < H / 8) ? src[s2][vi] : make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int s2 = 0; s2 < 2; ++s2) {
+      for (int k = 0; k < K; ++k) {
+        const int row = __shfl_sync(0xffffffffu, my_row[s2], k);
+        const int owner = __shfl_sync(0xffffffffu, my_owner[s2], k);
+        if (!has[s2]) continue;
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.peers[owner].packed) + (size_t)row * H);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int vi = vbase + lane + 32 * i;
+          if (vi < H / 8) dst[vi] = r[s2][i];
+        }
+      }
+    }
+  }
+  ptx::fence_proxy_async();  // packed rows are read by TMA
+  epi_bar();
+  if (p.eager && (uint32_t)etid < count * (uint32_t)K) {
+    const uint32_t t = t_first + (uint32_t)etid / (uint32_t)K, k = (uint32_t)etid % (uint32_t)K;
+    const int rowg = __ldcg(&p.dest_row[(size_t)t * K + k]);
+    const int owner = __ldcg(&p.topk_idx[(size_t)t * K + k]) / p.El;
+    const uint32_t le = (uint32_t)rowg / (uint32_t)p.cap_rows, pos = (uint32_t)rowg % (uint32_t)p.cap_rows;
+    const uint32_t j = pos / 128u, nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
+    fence_acqrel<S>();
+    const uint32_t prev = atom_add<S>(&p.peers[owner].tile_landed[(size_t)le * p.MT + j], 1u);
+    if (prev + 1u == 128u) {
+      fence_acqrel<S>();
+      queue_push<S>(p, p.peers[owner], nt1, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
+        a = task_word(FDMOE_TASK_FFN1, le, i);
+        b = j;
+        c = 128u;
+      });
+    }
+  }
+  if (p.eager) epi_bar();
+  if (etid == 0) {
+    fence_acqrel<S>();
+    const uint32_t done = atomicAdd(&p.peers[p.rank].ctl->pack_done, count) + count;
+    if (done == (uint32_t)p.T) gate_phase_finished<S>(p);
+  }
+}
+
+// ============================================================ FLUSH and FFN
 // FLUSH: every rank's gate phase is complete, so the per-expert row counts are
 // final.  Publishes FFN1 tasks for all tiles (or, in eager mode, only for the
 // partial last tile of each expert), ordered by expert so that tiles sharing
 // weights run close together.  Executed by the 256 epilogue threads.
 template <bool S>
-__device__ void flush_task(const FdmoeParams& p, SmemCtl& sc, int etid) {
+__device__ __noinline__ void flush_task(const FdmoeParams& p, SmemCtl& sc, int etid) {
   const FdmoePeer& me = p.peers[p.rank];
   const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
   fence_acqrel<S>();
@@ -588,8 +743,11 @@ __device__ void flush_task(const FdmoeParams& p, SmemCtl& sc, int etid) {
     s->a = task_word(FDMOE_TASK_FFN1, e, n);
     s->b = j;
     s->c = rows;
-    st_release<false>(&s->seq, t0 + idx + 1u);
   }
+  // one fence orders every payload above before every sequence word below
+  fence_acqrel<false>();
+  for (uint32_t idx = etid; idx < total; idx += kEpiThreads)
+    st_relaxed<false>(&me.slots[(t0 + idx) & (uint32_t)p.queue_mask].seq, t0 + idx + 1u);
   epi_bar();
   if (etid == 0) {
     fence_acqrel<false>();
@@ -598,107 +756,151 @@ __device__ void flush_task(const FdmoeParams& p, SmemCtl& sc, int etid) {
   }
 }
 
+// silu(g) * u with the fast exponential and reciprocal (relative error ~1e-6, far
+// below the bf16 rounding of the stored activation); g -> -inf gives -0.
 __device__ __forceinline__ float silu_mul(float g, float u) {
-  return g / (1.0f + __expf(-g)) * u;
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
+// Writes one 32-row x 64-byte chunk held as 16 packed words per thread (thread
+// = row) through the warp's staging buffer so that every global store
+// instruction covers 8 rows x 64 contiguous bytes instead of 32 rows x 16.
+// dst[i] / ok[i] describe row (lane >> 2) + 8 i: pointer to the chunk's first
+// byte in global memory and whether the row exists.
+__device__ __forceinline__ void store_chunk_coalesced(uint8_t* st, int lane, const uint32_t (&o)[16],
+                                                      uint8_t* const (&dst)[4], const bool (&ok)[4]) {
+  uint4* mine = reinterpret_cast<uint4*>(st + lane * 80);
+#pragma unroll
+  for (int v = 0; v < 4; ++v) mine[v] = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+  __syncwarp();
+  const int piece = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = (lane >> 2) + 8 * i;
+    const uint4 val = *reinterpret_cast<const uint4*>(st + r * 80 + piece * 16);
+    if (ok[i]) *reinterpret_cast<uint4*>(dst[i] + piece * 16) = val;
+  }
+  __syncwarp();
 }
 
 // FFN1 epilogue: act[row, n*128 + c] = silu(D[row, c]) * D[row, 128 + c].
-__device__ __forceinline__ void ffn1_epilogue(const FdmoeParams& p, uint32_t taddr, int q, int h,
-                                              int lane, uint32_t e, uint32_t j, uint32_t n,
+__device__ __forceinline__ void ffn1_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, int q, int h,
+                                              int lane, int ewarp, uint32_t e, uint32_t j, uint32_t n,
                                               uint32_t rows) {
-  const uint32_t row = q * 32 + lane;
-  bf16* dst = reinterpret_cast<bf16*>(p.act) +
-              ((size_t)e * p.cap_rows + (size_t)j * 128 + row) * p.I + n * FDMOE_TILE_N1 + h * 64;
+  uint8_t* st = sc.store_stage[ewarp];
+  uint8_t* dst[4];
+  bool ok[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t r = q * 32 + (lane >> 2) + 8 * i;
+    ok[i] = r < rows && !(p.debug_flags & 1);
+    dst[i] = reinterpret_cast<uint8_t*>(reinterpret_cast<bf16*>(p.act) +
+                                        ((size_t)e * p.cap_rows + (size_t)j * 128 + r) * p.I +
+                                        n * FDMOE_TILE_N1 + h * 64);
+  }
   const uint32_t tbase = taddr + ((uint32_t)(q * 32) << 16) + h * 64;
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
-    uint32_t g[32], u[32];
+    uint32_t g[32], u[32], o[16];
     ptx::tmem_ld_32x32(tbase + c * 32, g);
     ptx::tmem_ld_32x32(tbase + 128 + c * 32, u);
     ptx::tmem_ld_wait();
-    if (row < rows) {
+    prof_mark(p, sc, ewarp * 32 + lane, 10 + c * 3);
 #pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        uint4 o;
-        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          const int i = v * 8 + w * 2;
-          ow[w] = pack_bf16(silu_mul(__uint_as_float(g[i]), __uint_as_float(u[i])),
-                            silu_mul(__uint_as_float(g[i + 1]), __uint_as_float(u[i + 1])));
-        }
-        *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = o;
-      }
-    }
+    for (int w = 0; w < 16; ++w)
+      o[w] = pack_bf16(silu_mul(__uint_as_float(g[2 * w]), __uint_as_float(u[2 * w])),
+                       silu_mul(__uint_as_float(g[2 * w + 1]), __uint_as_float(u[2 * w + 1])));
+    uint8_t* d2[4] = {dst[0] + c * 64, dst[1] + c * 64, dst[2] + c * 64, dst[3] + c * 64};
+    prof_mark(p, sc, ewarp * 32 + lane, 11 + c * 3);
+    store_chunk_coalesced(st, lane, o, d2, ok);
+    prof_mark(p, sc, ewarp * 32 + lane, 12 + c * 3);
   }
 }
 
 // FFN2 epilogue: y[token, slot, n*256 + c] = D[row, c] * routing weight, stored
 // on the token's home rank.
-__device__ __forceinline__ void ffn2_epilogue(const FdmoeParams& p, uint32_t taddr, int q, int h,
-                                              int lane, uint32_t e, uint32_t j, uint32_t n,
+__device__ __forceinline__ void ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, int q, int h,
+                                              int lane, int ewarp, uint32_t e, uint32_t j, uint32_t n,
                                               uint32_t rows) {
+  uint8_t* st = sc.store_stage[ewarp];
   const uint32_t row = q * 32 + lane;
-  const bool valid = row < rows;
   float wgt = 0.f;
-  bf16* dst = nullptr;
-  if (valid) {
+  unsigned long long myptr = 0ull;
+  if (row < rows) {
     const uint4 mraw = ld_cg_u4(&p.peers[p.rank].meta[(size_t)e * p.cap_rows + (size_t)j * 128 + row]);
     const int token = (int)mraw.x, home = (int)mraw.y >> 8, slot = (int)mraw.y & 0xff;
     wgt = __uint_as_float(mraw.z);
-    dst = reinterpret_cast<bf16*>(p.peers[home].ystage) + ((size_t)token * p.K + slot) * p.H +
-          n * FDMOE_TILE_N2 + h * 128;
+    myptr = reinterpret_cast<unsigned long long>(reinterpret_cast<bf16*>(p.peers[home].ystage) +
+                                                 ((size_t)token * p.K + slot) * p.H + n * FDMOE_TILE_N2 + h * 128);
+  }
+  uint8_t* dst[4];
+  bool ok[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const unsigned long long pp = __shfl_sync(0xffffffffu, myptr, (lane >> 2) + 8 * i);
+    dst[i] = reinterpret_cast<uint8_t*>(pp);
+    ok[i] = pp != 0ull && !(p.debug_flags & 1);
   }
   const uint32_t tbase = taddr + ((uint32_t)(q * 32) << 16) + h * 128;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    uint32_t d[32];
+    uint32_t d[32], o[16];
     ptx::tmem_ld_32x32(tbase + c * 32, d);
     ptx::tmem_ld_wait();
-    if (valid) {
 #pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        uint4 o;
-        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          const int i = v * 8 + w * 2;
-          ow[w] = pack_bf16(__uint_as_float(d[i]) * wgt, __uint_as_float(d[i + 1]) * wgt);
-        }
-        *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = o;
-      }
-    }
+    for (int w = 0; w < 16; ++w)
+      o[w] = pack_bf16(__uint_as_float(d[2 * w]) * wgt, __uint_as_float(d[2 * w + 1]) * wgt);
+    uint8_t* d2[4] = {dst[0] + c * 64, dst[1] + c * 64, dst[2] + c * 64, dst[3] + c * 64};
+    store_chunk_coalesced(st, lane, o, d2, ok);
   }
 }
 
 // COMBINE: out[t, :] = sum over slots k = 0..K-1 (in that order, fp32) of
-// y[t, k, :], for the tokens of one group.  One warp per token.
-__device__ __forceinline__ void combine_task(const FdmoeParams& p, int ewarp, int lane, uint32_t g) {
+// y[t, k, :], for the tokens of one group.  One warp per token; the K loads of
+// a 16-byte column vector are issued together, then summed in slot order.
+__device__ __noinline__ void combine_task(const FdmoeParams& p, int ewarp, int lane, uint32_t g) {
   const int t_begin = (int)g * p.combine_group;
   const int t_end = min(t_begin + p.combine_group, p.T);
   const bf16* ys = reinterpret_cast<const bf16*>(p.peers[p.rank].ystage);
   bf16* out = reinterpret_cast<bf16*>(p.out);
-  const int nvec = p.H / 8;
+  const int nvec = p.H / 8, K = p.K;
   for (int t = t_begin + ewarp; t < t_end; t += kEpiThreads / 32) {
-    for (int v = lane; v < nvec; v += 32) {
-      float acc[8];
+    const bf16* yt = ys + (size_t)t * K * p.H;
+    for (int v = lane; v < nvec; v += 64) {
+      const bool two = v + 32 < nvec;
+      uint4 r0[FDMOE_MAX_TOPK], r1[FDMOE_MAX_TOPK];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int k = 0; k < p.K; ++k) {
-        const uint4 r = ld_cg_u4(ys + ((size_t)t * p.K + k) * p.H + v * 8);
-        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          acc[2 * i] += bf16_lo(w[i]);
-          acc[2 * i + 1] += bf16_hi(w[i]);
+      for (int k = 0; k < FDMOE_MAX_TOPK; ++k) {
+        if (k < K) {
+          r0[k] = ld_cg_u4(yt + (size_t)k * p.H + v * 8);
+          if (two) r1[k] = ld_cg_u4(yt + (size_t)k * p.H + (v + 32) * 8);
         }
       }
-      uint4 o;
-      o.x = pack_bf16(acc[0], acc[1]);
-      o.y = pack_bf16(acc[2], acc[3]);
-      o.z = pack_bf16(acc[4], acc[5]);
-      o.w = pack_bf16(acc[6], acc[7]);
-      *reinterpret_cast<uint4*>(out + (size_t)t * p.H + v * 8) = o;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        if (half == 1 && !two) break;
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+        for (int k = 0; k < FDMOE_MAX_TOPK; ++k) {
+          if (k < K) {
+            const uint4 r = half ? r1[k] : r0[k];
+            const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              acc[2 * i] += bf16_lo(w[i]);
+              acc[2 * i + 1] += bf16_hi(w[i]);
+            }
+          }
+        }
+        uint4 o;
+        o.x = pack_bf16(acc[0], acc[1]);
+        o.y = pack_bf16(acc[2], acc[3]);
+        o.z = pack_bf16(acc[4], acc[5]);
+        o.w = pack_bf16(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(out + (size_t)t * p.H + (v + half * 32) * 8) = o;
+      }
     }
   }
 }
@@ -744,6 +946,8 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
     ptx::prefetch_tmap(&p.tm_w13);
     ptx::prefetch_tmap(&p.tm_act);
     ptx::prefetch_tmap(&p.tm_w2);
+    ptx::prefetch_tmap(&p.tm_x);
+    ptx::prefetch_tmap(&p.tm_gate);
   }
   ptx::tcgen05_fence_before();
   __syncthreads();
@@ -771,22 +975,22 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
     __syncthreads();
   }
 
-  // =============================== phase A: gate tiles, claimed dynamically
-  if (p.mode != 2 && !sc.abort) {
-    const int n_tiles = (p.T + FDMOE_GATE_TOKENS - 1) / FDMOE_GATE_TOKENS;
-    if (n_tiles == 0 && blockIdx.x == 0 && tid == 0) gate_phase_finished<S>(p);
-    for (;;) {
-      if (tid == 0) sc.cur_tile = (int)atomicAdd(&ctl->gate_next, 1u);
-      __syncthreads();
-      const int tile = sc.cur_tile;
-      if (tile >= n_tiles || sc.abort) break;
-      gate_tile<S>(p, stage, sc, tile, n_tiles);
-      __syncthreads();
+  // ---- seed the queue: one GATE task per 128-token tile (nothing to gate: the
+  // rank's "gate phase" is finished at once, it may still serve its peers)
+  if (p.mode != 2 && !sc.abort && blockIdx.x == 0 && tid == 0) {
+    const uint32_t n_tiles = (uint32_t)((p.T + FDMOE_GATE_TOKENS - 1) / FDMOE_GATE_TOKENS);
+    if (n_tiles == 0) {
+      gate_phase_finished<S>(p);
+    } else {
+      queue_push<false>(p, me, n_tiles, [](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
+        a = FDMOE_TASK_GATE;
+        b = i;
+        c = 0;
+      });
     }
   }
-  __syncthreads();
 
-  // =============================== phase B: worker loop
+  // =============================== worker loop
   const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1), nt2 = (uint32_t)(p.H / FDMOE_TILE_N2);
   const uint32_t nkb1 = (uint32_t)(p.H / FDMOE_TILE_K), nkb2 = (uint32_t)(p.I / FDMOE_TILE_K);
 
@@ -814,11 +1018,13 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         const FdmoeSlot t = sc.ring[r];
         const uint32_t kind = t.a & 0xffu;
         if (kind == FDMOE_TASK_EXIT) break;
-        if (kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2) {
+        if (kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2 || kind == FDMOE_TASK_GATE) {
           const uint32_t e = (t.a >> 8) & 0xfffu, n = t.a >> 20, j = t.b;
-          const bool f1 = kind == FDMOE_TASK_FFN1;
-          const uint32_t nkb = f1 ? nkb1 : nkb2;
-          const int32_t arow = (int32_t)(e * (uint32_t)p.cap_rows + j * 128u);
+          const bool f1 = kind == FDMOE_TASK_FFN1, gt = kind == FDMOE_TASK_GATE;
+          const uint32_t nkb = (f1 || gt) ? nkb1 : nkb2;
+          const int32_t arow = gt ? (int32_t)(j * FDMOE_GATE_TOKENS) : (int32_t)(e * (uint32_t)p.cap_rows + j * 128u);
+          // bytes one GATE stage receives: both boxes are clamped to the tensor extents
+          const uint32_t gate_bytes = (uint32_t)(min(128, p.T) + min(128, p.E)) * FDMOE_TILE_K * 2u;
           ptx::fence_proxy_async();  // rows / activations were written with generic stores
           bool ok = true;
           for (uint32_t kb = 0; kb < nkb && ok; ++kb, ++stage_it) {
@@ -827,9 +1033,12 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
             if (!ok) break;
             uint8_t* sa = stage + s * kStageBytes;
             uint8_t* sb = sa + kStageA;
-            ptx::mbar_expect_tx(&sc.full_bar[s], kStageBytes);
+            ptx::mbar_expect_tx(&sc.full_bar[s], gt ? gate_bytes : (uint32_t)kStageBytes);
             const int32_t kx = (int32_t)(kb * FDMOE_TILE_K);
-            if (f1) {
+            if (gt) {
+              ptx::tma_load_2d(sa, &p.tm_x, &sc.full_bar[s], kx, arow);
+              ptx::tma_load_2d(sb, &p.tm_gate, &sc.full_bar[s], kx, 0);
+            } else if (f1) {
               ptx::tma_load_2d(sa, &p.tm_packed, &sc.full_bar[s], kx, arow);
               const int32_t brow = (int32_t)(e * 2u * (uint32_t)p.I + n * FDMOE_TILE_N1);
               ptx::tma_load_2d(sb, &p.tm_w13, &sc.full_bar[s], kx, brow);
@@ -848,7 +1057,8 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
     __syncwarp();
   } else if (warp == kWarpMma) {
     if (lane == 0) {
-      constexpr uint32_t idesc = ptx::make_idesc_bf16(128, 256);
+      constexpr uint32_t idesc256 = ptx::make_idesc_bf16(128, 256);
+      constexpr uint32_t idesc128 = ptx::make_idesc_bf16(128, 128);
       uint32_t stage_it = 0, tile_it = 0;
       for (uint32_t it = 0;; ++it) {
         const uint32_t r = it % kRing, ph = (it / kRing) & 1u;
@@ -856,8 +1066,9 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         const FdmoeSlot t = sc.ring[r];
         const uint32_t kind = t.a & 0xffu;
         if (kind == FDMOE_TASK_EXIT) break;
-        if (kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2) {
-          const uint32_t nkb = (kind == FDMOE_TASK_FFN1) ? nkb1 : nkb2;
+        if (kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2 || kind == FDMOE_TASK_GATE) {
+          const uint32_t nkb = (kind == FDMOE_TASK_FFN2) ? nkb2 : nkb1;
+          const uint32_t idesc = (kind == FDMOE_TASK_GATE) ? idesc128 : idesc256;
           const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
           ++tile_it;
           if (!wait_bar(p, sc, &sc.tmem_empty[acc], aph ^ 1u, FDMOE_ERR_TIMEOUT_TMEM)) break;
@@ -901,7 +1112,16 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       const uint32_t e = (t.a >> 8) & 0xfffu, n = t.a >> 20, j = t.b, rows = t.c;
       const uint32_t pt0 = (p.prof && etid == 0) ? prof_now() : 0u;
       uint32_t pt1 = pt0;
-      if (kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2) {
+      if (kind == FDMOE_TASK_GATE) {
+        const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
+        ++tile_it;
+        if (!epi_vote_all(wait_bar(p, sc, &sc.tmem_full[acc], aph, FDMOE_ERR_TIMEOUT_TMEM))) break;
+        if (p.prof && etid == 0) pt1 = prof_now();
+        ptx::tcgen05_fence_after();
+        gate_epilogue<S>(p, sc, tmem_base + acc * kAccCols, &sc.tmem_empty[acc], q, h, lane, etid, ewarp, j);
+      } else if (kind == FDMOE_TASK_PACK) {
+        pack_task<S>(p, sc, etid, ewarp, lane, j, rows);
+      } else if (kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2) {
         const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
         ++tile_it;
         if (!epi_vote_all(wait_bar(p, sc, &sc.tmem_full[acc], aph, FDMOE_ERR_TIMEOUT_TMEM))) break;
@@ -909,21 +1129,26 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         ptx::tcgen05_fence_after();
         const uint32_t taddr = tmem_base + acc * kAccCols;
         if (kind == FDMOE_TASK_FFN1)
-          ffn1_epilogue(p, taddr, q, h, lane, e, j, n, rows);
+          ffn1_epilogue(p, sc, taddr, q, h, lane, ewarp, e, j, n, rows);
         else
-          ffn2_epilogue(p, taddr, q, h, lane, e, j, n, rows);
+          ffn2_epilogue(p, sc, taddr, q, h, lane, ewarp, e, j, n, rows);
         ptx::tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&sc.tmem_empty[acc]);
+        const uint32_t pta = (p.prof && etid == 0) ? prof_now() : 0u;
 
         if (kind == FDMOE_TASK_FFN1) {
-          ptx::fence_proxy_async();  // the activation tile is read by TMA in FFN2
+          if (!(p.debug_flags & 4)) ptx::fence_proxy_async();  // the activation tile is read by TMA in FFN2
+          prof_mark(p, sc, etid, 20);
           epi_bar();
+          prof_mark(p, sc, etid, 21);
           if (etid == 0 && p.mode != 2) {
-            fence_acqrel<false>();
+            if (!(p.debug_flags & 2)) fence_acqrel<false>();
+            prof_mark(p, sc, etid, 22);
             const uint32_t prev = atomicAdd(&p.ffn1_done[(size_t)e * p.MT + j], 1u);
+            prof_mark(p, sc, etid, 23);
             if (prev == nt1 - 1u) {
-              fence_acqrel<false>();
+              if (!(p.debug_flags & 2)) fence_acqrel<false>();
               queue_push<false>(p, me, nt2, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
                 a = task_word(FDMOE_TASK_FFN2, e, i);
                 b = j;
@@ -936,9 +1161,9 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           if (etid == 0) {
             int last = 0;
             if (p.mode != 2) {
-              fence_acqrel<S>();
+              if (!(p.debug_flags & 2)) fence_acqrel<S>();
               const uint32_t prev = atomicAdd(&p.ffn2_done[(size_t)e * p.MT + j], 1u);
-              fence_acqrel<S>();
+              if (!(p.debug_flags & 2)) fence_acqrel<S>();
               last = prev == nt2 - 1u;
             }
             sc.flag = last;
@@ -971,6 +1196,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
             }
           }
         }
+        if (etid == 0) prof_event(p, sc, kind + 16u, pt1, pta, prof_now());
       } else if (kind == FDMOE_TASK_COMBINE) {
         combine_task(p, ewarp, lane, j);
         epi_bar();

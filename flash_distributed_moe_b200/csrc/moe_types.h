@@ -15,7 +15,8 @@ enum {
   FDMOE_TILE_N1 = 128,   // FFN1: activation columns per tile (MMA N = 2 * 128: gate + up)
   FDMOE_TILE_N2 = 256,   // FFN2: hidden columns per tile
   FDMOE_TILE_K = 64,     // one 128-byte swizzle atom of bf16 per stage
-  FDMOE_GATE_TOKENS = 32,  // tokens per gate tile
+  FDMOE_GATE_TOKENS = 128,  // tokens per gate tile (one tcgen05 M tile)
+  FDMOE_PACK_TOKENS = 16,   // tokens per PACK task
 };
 
 // Task kinds held by the global work queue.
@@ -28,6 +29,8 @@ enum {
   FDMOE_TASK_TESTA = 5,    // task-system self test: x[i] *= 2 over a chunk, then push TESTB
   FDMOE_TASK_TESTB = 6,    // task-system self test: x[i] += 1 over a chunk
   FDMOE_TASK_EXIT = 7,
+  FDMOE_TASK_GATE = 8,     // (token tile): gate GEMM, top-k, softmax, row reservation
+  FDMOE_TASK_PACK = 9,     // (first token, count): copy token rows into the owners' expert buffers
 };
 
 // Status codes written by the kernel (first error wins).
@@ -77,8 +80,8 @@ typedef struct {
   uint32_t ready[32];  // ready[r] = launch epoch of peer r (written by peer r)
   // --- per-launch counters: [launch_begin, launch_end) is zeroed before each launch
   uint32_t launch_begin;
-  uint32_t gate_next;        // next gate tile to claim
-  uint32_t gate_done;        // gate tiles finished on this rank
+  uint32_t pack_done;        // tokens of this rank whose rows are packed
+  uint32_t reserved0;
   uint32_t ranks_done;       // ranks whose gate phase is finished (incl. this one)
   uint32_t flush_done;
   uint32_t mtiles_total;     // m-tiles of this rank's experts this launch
@@ -113,6 +116,8 @@ typedef struct {
   FdmoeTensorMap tm_w13;     // [El*2I, H]         box 64 x 128
   FdmoeTensorMap tm_act;     // [El*cap_rows, I]   box 64 x 128
   FdmoeTensorMap tm_w2;      // [El*H, I]          box 64 x 256
+  FdmoeTensorMap tm_x;       // [T, H]             box 64 x min(128, T)   (rebuilt per launch)
+  FdmoeTensorMap tm_gate;    // [E, H]             box 64 x min(128, E)
 
   FdmoePeer peers[FDMOE_MAX_WORLD];  // peers[rank] is this rank itself
 
@@ -125,7 +130,9 @@ typedef struct {
   int32_t queue_mask;   // capacity - 1 (capacity is a power of two)
   int32_t combine_group;  // tokens per COMBINE task
   int32_t eager;        // publish full tiles as they land instead of at flush
-  int32_t mode;         // 0 full layer; 1 stop after gate; 2 static tasks only (no gate)
+  int32_t mode;         // 0 full layer; 2 static tasks only (no gate)
+  int32_t debug_flags;  // timing experiments only (results become invalid): 1 skip FFN stores,
+                        // 2 skip completion fences, 4 skip proxy fences
   uint32_t expected_static;  // mode 2: tasks pre-filled by the host
   uint32_t epoch;       // launch counter (identical on all ranks)
   uint64_t timeout_ns;  // budget of every device-side wait
@@ -136,10 +143,12 @@ typedef struct {
   void* act;            // bf16 [El * cap_rows, I]
   int32_t* topk_idx;    // [max_tokens, K]
   float* topk_w;        // [max_tokens, K]
+  int32_t* dest_row;    // [max_tokens, K] row of (token, slot) in its owner's expert buffers
   uint32_t* ffn1_done;  // [El * MT]
   uint32_t* ffn2_done;  // [El * MT]
   uint32_t* status_host;  // mapped pinned word: first error code, readable without a sync
   int32_t* test_buf;    // task-system self test payload
+  float* debug_logits;  // optional dump of the tensor-core gate logits [T, 128] (NULL = off)
   uint32_t* prof;       // optional event trace, FDMOE_PROF_EVENTS x 4 words per CTA (NULL = off)
 } FdmoeParams;
 

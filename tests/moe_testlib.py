@@ -38,12 +38,12 @@ def rel_l2(a: np.ndarray, b: np.ndarray) -> float:
 
 def assert_close_bf16(got: np.ndarray, ref: np.ndarray, what: str) -> None:
     """North-star bound for bf16 results: max-abs 2e-2 and rel-L2 1e-2.  bf16 keeps 8 significant bits, so
-    one ulp of a value v is up to 2^-7 |v|; results and the staged per-slot rows are rounded to bf16, which
-    for |v| > 2.56 alone exceeds 2e-2.  For such elements the absolute bound is widened to one bf16 ulp of
-    the value.  The synthetic N(0,0.02) layers of the benchmark never reach that size, so there the plain
+    one ulp of a value v is up to 2^-7 |v|; the result and the K staged per-slot rows it is summed from
+    are all rounded to bf16, which for |v| > 2.56 alone exceeds 2e-2.  For such elements the absolute
+    bound is widened to two bf16 ulps of the value (2^-6 |v|).  The synthetic N(0,0.02) layers of the benchmark never reach that size, so there the plain
     2e-2 bound is what is enforced; the widening matters only for the reference's U(-0.1,0.1) test stream."""
     err = np.abs(got.astype(np.float64) - ref.astype(np.float64))
-    tol = np.maximum(MAX_ABS, np.abs(ref) * 2.0 ** -7)
+    tol = np.maximum(MAX_ABS, np.abs(ref) * 2.0 ** -6)
     worst = float((err / tol).max()) if err.size else 0.0
     rl2 = rel_l2(got, ref)
     assert worst <= 1.0 and rl2 <= REL_L2, f"{what}: max-abs {err.max():.3e} ({worst:.2f}x tolerance), rel-L2 {rl2:.3e}"

@@ -36,9 +36,11 @@ def check_layer(shape, x, gate, w13, w2, max_tokens, golden=None, inplace=False,
         layer.close()
 
     if check_stages:
-        # --- gate: indices bit-exact (the gate GEMM reproduces the reference's fp32 order), weights to 1e-6
+        # --- gate: indices bit-exact, in the reference's order, with no near-tie exclusion (nearly tied
+        # tokens are recomputed in the reference's fp32 order on the device); weights to 1e-5, the
+        # tolerance of the reference's own gate test (test/common/utils.h:27, moeGateTest.hip:62-109)
         assert np.array_equal(st["idx"], o_idx), f"top-k mismatch on {(st['idx'] != o_idx).any(1).sum()} tokens"
-        assert np.abs(st["w"] - o_w).max() <= 1e-6
+        assert np.abs(st["w"] - o_w).max() <= 1e-5
         # --- routing: per-expert row counts and the (token, slot) set of each expert
         cap = layer.cap_rows
         for e in range(shape.experts):
@@ -57,7 +59,7 @@ def check_layer(shape, x, gate, w13, w2, max_tokens, golden=None, inplace=False,
             toks, slots = m[:, 0], m[:, 1] & 0xff
             wts = m[:, 2].copy().view(np.float32)
             assert torch.equal(st["packed"][e * cap:e * cap + n], x[torch.from_numpy(toks.astype(np.int64))])
-            assert np.abs(wts - o_w[toks, slots]).max() <= 1e-6
+            assert np.abs(wts - o_w[toks, slots]).max() <= 1e-5
             act_got.append(tl.f32(st["act"][e * cap:e * cap + n]))
             act_ref.append(o_act[toks, slots])
         tl.assert_close_bf16(np.concatenate(act_got), np.concatenate(act_ref), "FFN1 activations")
