@@ -180,6 +180,7 @@ class MoeKernelLauncher final : public moe::IMoeKernelLauncher {
   int32_t* topk_idx_ = nullptr;
   float* topk_w_ = nullptr;
   int32_t* dest_row_ = nullptr;
+  uint8_t* tok_flag_ = nullptr;
   uint32_t* status_host_ = nullptr;
   uint32_t* status_dev_ = nullptr;
   // fp32 I/O mode: bf16 copies of the weights and token staging
@@ -198,7 +199,7 @@ void MoeKernelLauncher::FreeAll() {
   for (int r = 0; r < (int)peer_bases_.size(); ++r)
     if (r != rank_ && peer_bases_[r]) cudaIpcCloseMemHandle(peer_bases_[r]);
   peer_bases_.clear();
-  void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, dest_row_, gate_bf16_, w13_bf16_, w2_bf16_,
+  void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, dest_row_, tok_flag_, gate_bf16_, w13_bf16_, w2_bf16_,
                   tok_bf16_, out_bf16_, host_in_dev_, host_out_dev_, prof_, debug_logits_};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -207,6 +208,7 @@ void MoeKernelLauncher::FreeAll() {
   topk_idx_ = nullptr;
   topk_w_ = nullptr;
   dest_row_ = nullptr;
+  tok_flag_ = nullptr;
   gate_bf16_ = w13_bf16_ = w2_bf16_ = tok_bf16_ = out_bf16_ = host_in_dev_ = host_out_dev_ = nullptr;
   prof_ = nullptr;
   debug_logits_ = nullptr;
@@ -223,7 +225,7 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
     MOE_ERROR_LOG("bad rank/world %d/%d (world size 1..%d)", rank, world, FDMOE_MAX_WORLD);
     return cudaErrorInvalidValue;
   }
-  if (cfg.hiddenSize <= 0 || cfg.hiddenSize % FDMOE_TILE_N2 != 0 || cfg.expertIntermediateSize <= 0 ||
+  if (cfg.hiddenSize <= 0 || cfg.hiddenSize % FDMOE_TILE_N2 != 0 || cfg.hiddenSize > FDMOE_MAX_HIDDEN || cfg.expertIntermediateSize <= 0 ||
       cfg.expertIntermediateSize % FDMOE_TILE_N1 != 0 || cfg.expertsNum <= 0 ||
       cfg.expertsNum > FDMOE_MAX_EXPERTS || cfg.expertsNum % world != 0 || cfg.topk <= 0 ||
       cfg.topk > FDMOE_MAX_TOPK || cfg.topk > cfg.expertsNum ||
@@ -314,6 +316,7 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&topk_idx_), std::max<size_t>(4, (size_t)maxTokens * g_.K * 4)));
   CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&topk_w_), std::max<size_t>(4, (size_t)maxTokens * g_.K * 4)));
   CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&dest_row_), std::max<size_t>(4, (size_t)maxTokens * g_.K * 4)));
+  CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&tok_flag_), std::max<size_t>(16, (size_t)maxTokens)));
   CUDA_ERROR_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped));
   memset(status_host_, 0, 64);
   CUDA_ERROR_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_), status_host_, 0));
@@ -406,6 +409,7 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   params_.topk_idx = topk_idx_;
   params_.topk_w = topk_w_;
   params_.dest_row = dest_row_;
+  params_.tok_flag = tok_flag_;
   params_.ffn1_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn1_done);
   params_.ffn2_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn2_done);
   params_.status_host = status_dev_;

@@ -36,7 +36,7 @@ constexpr int kThreads = 384;  // 12 warps
 constexpr int kWarpSched = 0;  // pops global tickets, feeds the CTA task ring
 constexpr int kWarpTma = 1;    // issues TMA loads
 constexpr int kWarpMma = 2;    // issues tcgen05.mma
-constexpr int kWarpTmem = 3;   // allocates / frees TMEM
+constexpr int kWarpTmem = 3;   // allocates / frees TMEM; completion warp in between
 constexpr int kWarpEpi0 = 4;   // warps 4..11: epilogues and SIMT tasks
 constexpr int kEpiThreads = 256;
 
@@ -45,6 +45,8 @@ constexpr int kStageA = FDMOE_TILE_M * FDMOE_TILE_K * 2;  // 16 KB
 constexpr int kStageB = 256 * FDMOE_TILE_K * 2;           // 32 KB
 constexpr int kStageBytes = kStageA + kStageB;            // 48 KB
 constexpr int kRing = 3;
+constexpr int kPrefetch = 8;  // k-blocks by which the L2 prefetch of weights runs ahead
+constexpr int kDone = 4;  // depth of the hand-off ring to the completion warp
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = 256;
 
@@ -56,6 +58,9 @@ struct __align__(16) SmemCtl {
   uint64_t ring_full[kRing];
   uint64_t ring_empty[kRing];
   FdmoeSlot ring[kRing];
+  uint64_t done_full[kDone];   // epilogue -> completion warp: a tile's stores are issued
+  uint64_t done_empty[kDone];
+  FdmoeSlot done_ring[kDone];
   uint32_t tmem_base;
   volatile uint32_t abort;
   int32_t flag;
@@ -63,26 +68,29 @@ struct __align__(16) SmemCtl {
   uint32_t q_total;
   uint32_t prof_n;
   uint32_t n_flagged;
-  // flush scratch (per local expert)
-  uint32_t pre[132];
-  uint32_t full_tiles[128];
-  uint32_t rem_rows[128];
+  uint32_t pre[16];  // flush scratch: per-warp totals
   // The epilogue group runs one task at a time, so the scratch of a GATE task
   // and the store staging of an FFN task share storage.  16-byte aligned: the
   // staging buffer is accessed with 16-byte vector loads and stores.
   union alignas(16) {
     struct {
-      // gate-tile scratch (per expert / per token of the tile)
+      // GATE task scratch (per expert / per token of the tile)
       uint32_t cnt[128];
       uint32_t base[128];
       uint32_t flagged[FDMOE_GATE_TOKENS];
-      float exact[8][128];                      // exact logits of the tokens being recomputed
-      float half_v[2][FDMOE_GATE_TOKENS][9];    // top-9 of each 64-column half
-      uint8_t half_i[2][FDMOE_GATE_TOKENS][12];
-      float top_v[FDMOE_GATE_TOKENS][9];        // merged top-9 logits, descending
+      uint8_t isflag[FDMOE_GATE_TOKENS];
+      float logit_tile[32][132];                // one 32-token quarter of the logits (padded rows)
+      float top_v[FDMOE_GATE_TOKENS][9];        // top-9 logits per token, descending
       uint8_t top_i[FDMOE_GATE_TOKENS][12];
       float tk_w[FDMOE_GATE_TOKENS][FDMOE_MAX_TOPK];
       uint8_t lpos[FDMOE_GATE_TOKENS][FDMOE_MAX_TOPK];
+    };
+    struct {
+      // GATEFIX task scratch: two token rows and their exact logits
+      uint4 xrow[2][FDMOE_MAX_HIDDEN / 8];
+      float exact[2][128];
+      int32_t fix_row[2][FDMOE_MAX_TOPK];
+      int32_t fix_owner[2][FDMOE_MAX_TOPK];
     };
     // FFN epilogues: per-warp staging of a 32-row x 64-byte chunk (80-byte pitch
     // keeps the 16-byte accesses of a quarter warp on distinct banks)
@@ -92,6 +100,8 @@ struct __align__(16) SmemCtl {
 
 constexpr int kSmemBytes = kStages * kStageBytes + (int)sizeof(SmemCtl) + 1024;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA exceeds the sm_100 limit");
+static_assert(offsetof(SmemCtl, xrow) % 16 == 0 && offsetof(SmemCtl, logit_tile) % 16 == 0 && (132 * 4) % 16 == 0,
+              "vector accesses to the gate scratch need 16-byte alignment");
 static_assert(offsetof(SmemCtl, store_stage) % 16 == 0 && (32 * 80) % 16 == 0 && 80 % 16 == 0,
               "store staging must keep 16-byte alignment for every warp and row");
 static_assert(offsetof(SmemCtl, full_bar) % 8 == 0 && offsetof(SmemCtl, ring) % 16 == 0, "barrier / ring alignment");
@@ -323,83 +333,59 @@ __device__ void gate_phase_finished(const FdmoeParams& p) {
 }
 
 // ===================================================================== GATE
-// Top-9 of the 64 logits one thread holds (columns c0..c0+63 of its token row,
-// as two raw 32-word TMEM loads), descending, the lower column winning ties.
-// Branch-free selection rounds; a selected entry is replaced by -inf.
-__device__ __forceinline__ void top9_of_64(uint32_t (&lo)[32], uint32_t (&hi)[32], int c0, int E, float (&tv)[9],
-                                           int (&ti)[9]) {
-  const uint32_t ninf = 0xff800000u;
-#pragma unroll
-  for (int c = 0; c < 32; ++c) {
-    if (c0 + c >= E) lo[c] = ninf;
-    if (c0 + 32 + c >= E) hi[c] = ninf;
-  }
-#pragma unroll
-  for (int r = 0; r < 9; ++r) {
-    float b0 = -INFINITY, b1 = -INFINITY;
-    int i0 = 255, i1 = 255;
-#pragma unroll
-    for (int c = 0; c < 32; ++c) {
-      const float f0 = __uint_as_float(lo[c]), f1 = __uint_as_float(hi[c]);
-      const bool g0 = f0 > b0;
-      b0 = g0 ? f0 : b0;
-      i0 = g0 ? c : i0;
-      const bool g1 = f1 > b1;
-      b1 = g1 ? f1 : b1;
-      i1 = g1 ? 32 + c : i1;
-    }
-    const bool up = b1 > b0;  // the upper chain wins only when strictly greater
-    const float bv = up ? b1 : b0;
-    const int bi = up ? i1 : i0;
-    tv[r] = bv;
-    ti[r] = bi == 255 ? 255 : c0 + bi;
-#pragma unroll
-    for (int c = 0; c < 32; ++c) {
-      if (c == bi) lo[c] = ninf;
-      if (32 + c == bi) hi[c] = ninf;
-    }
-  }
+// Monotonic unsigned key of a float (larger float <=> larger key; -0 counts as +0).
+__device__ __forceinline__ uint32_t order_key(float f) {
+  const uint32_t u = __float_as_uint(f + 0.0f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_to_float(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
 }
 
-// Exact gate logits of up to four tokens for one expert: fp32 FMAs with k
-// strictly ascending per output (bf16 x bf16 products are exact in fp32, so this
-// equals the reference's `acc += a*b` bit for bit; reference refGemm.h:16-27).
-// The four accumulation chains are independent, which hides the FMA latency;
-// the weight row is prefetched 64 elements ahead.
-__device__ __forceinline__ void exact_logits4(const FdmoeParams& p, const int (&tok)[4], int e, float (&acc)[4]) {
-  const int H = p.H;
-  const uint4* w = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.gate_w) + (size_t)e * H);
-  const uint4* x[4];
+// Warp-wide top-k of four rows of 128 logits at once (lane l owns experts l,
+// l+32, l+64, l+96 of each row), descending, the lower index winning ties
+// (reference refTopk.h:36-58).  Each round is one warp-wide max over the value
+// keys and one warp-wide min over the indices that hold that value
+// (redux.sync), for four independent rows.  Lane k < K ends up holding slot k.
+__device__ __forceinline__ void topk_warp4(const float* r0, int pitch, int E, int K, int lane, float (&myv)[4],
+                                           int (&myi)[4]) {
+  uint32_t key[4][4];  // key 0 marks "taken / not an expert" (no finite float maps to it)
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    x[i] = reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(p.x) + (size_t)tok[i] * H);
-    acc[i] = 0.f;
-  }
-  uint4 wc[8], wn[8];
+  for (int r = 0; r < 4; ++r) {
 #pragma unroll
-  for (int u = 0; u < 8; ++u) wc[u] = __ldg(w + u);
-  const int nblk = H / 64;
-  for (int blk = 0; blk < nblk; ++blk) {
-    if (blk + 1 < nblk) {
-#pragma unroll
-      for (int u = 0; u < 8; ++u) wn[u] = __ldg(w + (blk + 1) * 8 + u);
+    for (int i = 0; i < 4; ++i) {
+      const int e = lane + 32 * i;
+      key[r][i] = (e < E) ? max(order_key(r0[r * pitch + e]), 1u) : 0u;
     }
+    myv[r] = 0.f;
+    myi[r] = 0;
+  }
+  for (int k = 0; k < K; ++k) {
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const uint32_t ww[4] = {wc[u].x, wc[u].y, wc[u].z, wc[u].w};
+    for (int r = 0; r < 4; ++r) {
+      // local best: ascending i is ascending expert index, strict '>' keeps the lower one
+      uint32_t bk = key[r][0];
+      int bi = 0;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint4 xv = x[i][blk * 8 + u];
-        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          acc[i] = fmaf(bf16_lo(xw[j]), bf16_lo(ww[j]), acc[i]);
-          acc[i] = fmaf(bf16_hi(xw[j]), bf16_hi(ww[j]), acc[i]);
+      for (int i = 1; i < 4; ++i) {
+        if (key[r][i] > bk) {
+          bk = key[r][i];
+          bi = i;
         }
       }
-    }
+      const uint32_t m = __reduce_max_sync(0xffffffffu, bk);
+      const uint32_t cand = (bk == m) ? (uint32_t)(lane + 32 * bi) : 0xffffffffu;
+      const uint32_t win = __reduce_min_sync(0xffffffffu, cand);
+      if ((win & 31u) == (uint32_t)lane) {
 #pragma unroll
-    for (int u = 0; u < 8; ++u) wc[u] = wn[u];
+        for (int i = 0; i < 4; ++i)
+          if ((win >> 5) == (uint32_t)i) key[r][i] = 0u;
+      }
+      if (lane == k) {
+        myv[r] = key_to_float(m);
+        myi[r] = (int)win;
+      }
+    }
   }
 }
 
@@ -447,113 +433,79 @@ __device__ __forceinline__ void topk_warp(const float* logits, int E, int K, int
 
 // Epilogue of a GATE task (256 threads).  The accumulator holds the logits of
 // 128 tokens (TMEM lanes) x 128 experts (columns) as computed by the tensor
-// cores, whose accumulation order is not the reference's.  A token whose
-// leading nine logits contain an adjacent pair closer than `tau` (2.5e-4 of the
-// logit scale, an order of magnitude above the rounding noise of either
-// accumulation order over a few thousand terms) is recomputed exactly; for all
-// other tokens both orders select the same experts in the same order.
+// cores, whose accumulation order is not the reference's.  Measured on B200 the
+// two orders differ by at most 2.7e-9 * H of the logit scale.  A token whose
+// leading nine logits contain an adjacent pair closer than tau = 6e-8 * H of the
+// scale (more than ten times that difference on each side) is handed to a
+// GATEFIX task, which recomputes its logits in the reference's order; for every
+// other token both orders select the same experts in the same order.
 template <bool S>
 __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, uint64_t* tmem_empty_bar,
-                              int q, int h, int lane, int etid, int ewarp, uint32_t tile) {
+                                           int q, int h, int lane, int etid, int ewarp, uint32_t tile) {
   const int E = p.E, K = p.K;
   const int t0 = (int)tile * FDMOE_GATE_TOKENS;
   const int nt = min(FDMOE_GATE_TOKENS, p.T - t0);
-  const int row = q * 32 + lane;
+  const int kk = min(E, 9);
 
   if (etid < 128) sc.cnt[etid] = 0;
   if (etid == 0) sc.n_flagged = 0;
-  {
-    uint32_t vlo[32], vhi[32];
-    const uint32_t tb = taddr + ((uint32_t)(q * 32) << 16) + h * 64;
-    ptx::tmem_ld_32x32(tb, vlo);
-    ptx::tmem_ld_32x32(tb + 32, vhi);
-    ptx::tmem_ld_wait();
-    ptx::tcgen05_fence_before();
-    __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(tmem_empty_bar);  // accumulator is free again
-    if (p.debug_logits && row < nt) {
+  // ---- four passes, one per TMEM lane quadrant: the two warps that may read the
+  // quadrant spill its 32 rows to shared memory, then every warp extracts the
+  // top-9 of four rows with warp-wide arg-max rounds
+  prof_mark(p, sc, etid, 40);
+  for (int pass = 0; pass < 4; ++pass) {
+    if (q == pass) {
+      uint32_t v[32];
+      const uint32_t tb = taddr + ((uint32_t)(q * 32) << 16) + h * 64;
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        p.debug_logits[(size_t)(t0 + row) * 128 + h * 64 + c] = __uint_as_float(vlo[c]);
-        p.debug_logits[(size_t)(t0 + row) * 128 + h * 64 + 32 + c] = __uint_as_float(vhi[c]);
+      for (int c2 = 0; c2 < 2; ++c2) {
+        ptx::tmem_ld_32x32(tb + c2 * 32, v);
+        ptx::tmem_ld_wait();
+        float* dst = &sc.logit_tile[lane][h * 64 + c2 * 32];
+#pragma unroll
+        for (int c = 0; c < 32; c += 4)
+          *reinterpret_cast<uint4*>(dst + c) = make_uint4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+        if (p.debug_logits && q * 32 + lane < nt) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c)
+            p.debug_logits[(size_t)(t0 + q * 32 + lane) * 128 + h * 64 + c2 * 32 + c] = __uint_as_float(v[c]);
+        }
+      }
+      ptx::tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tmem_empty_bar);  // this warp is done with the accumulator
+    }
+    epi_bar();
+    prof_mark(p, sc, etid, 41);
+    {
+      float myv[4];
+      int myi[4];
+      topk_warp4(sc.logit_tile[ewarp * 4], 132, E, kk, lane, myv, myi);
+      if (lane < kk) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          sc.top_v[pass * 32 + ewarp * 4 + r][lane] = myv[r];
+          sc.top_i[pass * 32 + ewarp * 4 + r][lane] = (uint8_t)myi[r];
+        }
       }
     }
-    prof_mark(p, sc, etid, 1);
-    float tv[9];
-    int ti[9];
-    top9_of_64(vlo, vhi, h * 64, E, tv, ti);
-    prof_mark(p, sc, etid, 2);
-#pragma unroll
-    for (int j = 0; j < 9; ++j) {
-      sc.half_v[h][row][j] = tv[j];
-      sc.half_i[h][row][j] = (uint8_t)ti[j];
-    }
+    epi_bar();
+    prof_mark(p, sc, etid, 42);
   }
-  epi_bar();
-  {
-    // merge by rank: position = own rank + number of partner entries ahead of it;
-    // the lower half (lower expert indices) wins ties
-    const int o = h ^ 1;
-#pragma unroll
-    for (int j = 0; j < 9; ++j) {
-      const float mv = sc.half_v[h][row][j];
-      int pos = j;
-#pragma unroll
-      for (int m = 0; m < 9; ++m) {
-        const float ov = sc.half_v[o][row][m];
-        pos += (h == 0) ? (ov > mv) : (ov >= mv);
-      }
-      if (pos < 9 && mv > -INFINITY) {
-        sc.top_v[row][pos] = mv;
-        sc.top_i[row][pos] = sc.half_i[h][row][j];
-      }
-    }
-  }
-  epi_bar();
-  if (etid < nt) {
-    // etid == row for the first four epilogue warps
-    const int cand = min(E, 9);
-    const float tau = 2.5e-4f * fmaxf(1.0f, fabsf(sc.top_v[etid][0]));
+  prof_mark(p, sc, etid, 2);
+  if (etid < FDMOE_GATE_TOKENS) {
     bool tie = false;
-    for (int j = 0; j + 1 < cand; ++j) tie |= (sc.top_v[etid][j] - sc.top_v[etid][j + 1]) < tau;
-    if (tie) sc.flagged[atomicAdd(&sc.n_flagged, 1u)] = (uint32_t)etid;
+    if (etid < nt) {
+      const float tau = 6e-8f * (float)p.H * fmaxf(1.0f, fabsf(sc.top_v[etid][0]));
+      for (int j = 0; j + 1 < kk; ++j) tie |= (sc.top_v[etid][j] - sc.top_v[etid][j + 1]) < tau;
+      if (tie) sc.flagged[atomicAdd(&sc.n_flagged, 1u)] = (uint32_t)etid;
+      p.tok_flag[t0 + etid] = tie ? 1 : 0;
+    }
+    sc.isflag[etid] = tie ? 1 : 0;
   }
   epi_bar();
   prof_mark(p, sc, etid, 3);
-  // exact recompute of the flagged tokens, eight per pass: each half of the
-  // group takes four tokens, one expert per thread; then one warp per token selects
-  {
-    const uint32_t nf = sc.n_flagged;
-    const int half = etid >> 7, e = etid & 127;
-    for (uint32_t f0 = 0; f0 < nf; f0 += 8) {
-      int tok[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t f = f0 + (uint32_t)(half * 4 + i);
-        tok[i] = t0 + (int)sc.flagged[f < nf ? f : f0];  // out-of-range entries repeat a valid token
-      }
-      if (f0 + (uint32_t)(half * 4) < nf && e < E) {
-        float acc[4];
-        exact_logits4(p, tok, e, acc);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) sc.exact[half * 4 + i][e] = acc[i];
-      }
-      epi_bar();
-      if (f0 + (uint32_t)ewarp < nf) {
-        const int tk = (int)sc.flagged[f0 + ewarp];
-        float myv;
-        int myi;
-        topk_warp(sc.exact[ewarp], E, K, lane, myv, myi);
-        if (lane < K) {
-          sc.top_v[tk][lane] = myv;
-          sc.top_i[tk][lane] = (uint8_t)myi;
-        }
-      }
-      epi_bar();
-    }
-  }
-  prof_mark(p, sc, etid, 4);
-  if (etid < nt) {
+  if (etid < nt && !sc.isflag[etid]) {
     // softmax over the K kept logits, in double, in the reference's order: the
     // values are descending, so the running max is the first one and the sum is
     // 1 + e_1 + e_2 + ... (reference refSoftmax.h:23-50)
@@ -593,7 +545,7 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
   }
   epi_bar();
   prof_mark(p, sc, etid, 6);
-  if (etid < nt && !sc.abort) {
+  if (etid < nt && !sc.isflag[etid] && !sc.abort) {
     for (int k = 0; k < K; ++k) {
       const int e = sc.top_i[etid][k];
       const int owner = e / p.El, le = e - owner * p.El;
@@ -609,10 +561,18 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
   if (etid == 0 && !sc.abort) {
     fence_acqrel<S>();
     const uint32_t ngroups = (uint32_t)((nt + FDMOE_PACK_TOKENS - 1) / FDMOE_PACK_TOKENS);
-    queue_push<false>(p, p.peers[p.rank], ngroups, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
-      a = FDMOE_TASK_PACK;
-      b = (uint32_t)t0 + i * FDMOE_PACK_TOKENS;
-      c = (uint32_t)min(FDMOE_PACK_TOKENS, nt - (int)i * FDMOE_PACK_TOKENS);
+    const uint32_t nf = sc.n_flagged, nfix = (nf + 1u) / 2u;
+    queue_push<false>(p, p.peers[p.rank], ngroups + nfix, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
+      if (i < nfix) {  // the slow tasks first
+        a = FDMOE_TASK_GATEFIX;
+        b = (uint32_t)t0 + sc.flagged[2 * i];
+        c = (2 * i + 1 < nf) ? (uint32_t)t0 + sc.flagged[2 * i + 1] : 0xffffffffu;
+      } else {
+        const uint32_t g = i - nfix;
+        a = FDMOE_TASK_PACK;
+        b = (uint32_t)t0 + g * FDMOE_PACK_TOKENS;
+        c = (uint32_t)min(FDMOE_PACK_TOKENS, nt - (int)g * FDMOE_PACK_TOKENS);
+      }
     });
   }
 }
@@ -628,7 +588,9 @@ __device__ __noinline__ void pack_task(const FdmoeParams& p, SmemCtl& sc, int et
   const int H = p.H, K = p.K;
   const bf16* x = reinterpret_cast<const bf16*>(p.x);
   // a warp takes tokens ewarp and ewarp + 8 of the group and keeps the loads of both in flight
-  const bool has[2] = {(uint32_t)ewarp < count, (uint32_t)ewarp + 8u < count};
+  // (tokens handed to a GATEFIX task are packed there)
+  const bool has[2] = {(uint32_t)ewarp < count && !__ldcg(&p.tok_flag[t_first + ewarp]),
+                       (uint32_t)ewarp + 8u < count && !__ldcg(&p.tok_flag[t_first + ewarp + 8])};
   // lane k < K keeps the destination of slot k of both tokens; broadcast by shuffle when needed
   int my_row[2] = {0, 0}, my_owner[2] = {0, 0};
   const uint4* src[2];
@@ -668,7 +630,8 @@ __device__ __noinline__ void pack_task(const FdmoeParams& p, SmemCtl& sc, int et
   }
   ptx::fence_proxy_async();  // packed rows are read by TMA
   epi_bar();
-  if (p.eager && (uint32_t)etid < count * (uint32_t)K) {
+  if (p.eager && (uint32_t)etid < count * (uint32_t)K &&
+      !__ldcg(&p.tok_flag[t_first + (uint32_t)etid / (uint32_t)K])) {
     const uint32_t t = t_first + (uint32_t)etid / (uint32_t)K, k = (uint32_t)etid % (uint32_t)K;
     const int rowg = __ldcg(&p.dest_row[(size_t)t * K + k]);
     const int owner = __ldcg(&p.topk_idx[(size_t)t * K + k]) / p.El;
@@ -687,10 +650,130 @@ __device__ __noinline__ void pack_task(const FdmoeParams& p, SmemCtl& sc, int et
   }
   if (p.eager) epi_bar();
   if (etid == 0) {
+    uint32_t mine = 0;
+    for (uint32_t i = 0; i < count; ++i) mine += __ldcg(&p.tok_flag[t_first + i]) ? 0u : 1u;
     fence_acqrel<S>();
-    const uint32_t done = atomicAdd(&p.peers[p.rank].ctl->pack_done, count) + count;
+    const uint32_t done = atomicAdd(&p.peers[p.rank].ctl->pack_done, mine) + mine;
+    if (mine && done == (uint32_t)p.T) gate_phase_finished<S>(p);
+  }
+}
+
+// ================================================================== GATEFIX
+// Up to two tokens whose leading tensor-core logits were nearly tied: all E
+// logits are recomputed with fp32 FMAs in the reference's order (128 threads per
+// token, one expert each), then top-k, softmax, row reservation and the pack of
+// the token rows, i.e. everything GATE and PACK do for the other tokens.
+template <bool S>
+__device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uint8_t* stage, uint32_t& stage_it,
+                                          int etid, int ewarp, int lane, uint32_t tok_a, uint32_t tok_b) {
+  const int H = p.H, E = p.E, K = p.K;
+  const int half = etid >> 7, e = etid & 127;
+  const uint32_t tok = half ? tok_b : tok_a;
+  const bool live = tok != 0xffffffffu;
+  const bf16* x = reinterpret_cast<const bf16*>(p.x);
+  if (live) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)tok * H);
+    for (int v = e; v < H / 8; v += 128) sc.xrow[half][v] = src[v];
+  }
+  epi_bar();
+  prof_mark(p, sc, etid, 30);
+  // Exact logits: fp32 FMAs with k strictly ascending per output (bf16 x bf16
+  // products are exact in fp32, so this equals the reference's `acc += a*b` bit
+  // for bit; reference refGemm.h:16-27).  The gate weights arrive 64 columns at a
+  // time through the stage ring (TMA, 128-byte swizzle: 16-byte chunk c of row r
+  // sits at chunk c ^ (r & 7)); the token row is broadcast from shared memory.
+  {
+    float acc = 0.f;
+    const uint32_t nkb = (uint32_t)(H / FDMOE_TILE_K);
+    for (uint32_t kb = 0; kb < nkb; ++kb, ++stage_it) {
+      const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
+      if (!epi_vote_all(wait_bar(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE))) return false;
+      if (live && e < E) {
+        const uint4* tile = reinterpret_cast<const uint4*>(stage + s * kStageBytes);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 wv = tile[e * 8 + (c ^ (e & 7))];
+          const uint4 xv = sc.xrow[half][kb * 8 + c];
+          const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+          const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc = fmaf(bf16_lo(xw[j]), bf16_lo(ww[j]), acc);
+            acc = fmaf(bf16_hi(xw[j]), bf16_hi(ww[j]), acc);
+          }
+        }
+      }
+      epi_bar();  // every thread has read the stage
+      if (etid == 0) ptx::mbar_arrive(&sc.empty_bar[s]);
+    }
+    if (live && e < E) sc.exact[half][e] = acc;
+  }
+  epi_bar();
+  prof_mark(p, sc, etid, 31);
+  if (live && (ewarp & 3) == 0) {
+    float myv;
+    int myi;
+    topk_warp(sc.exact[half], E, K, lane, myv, myi);
+    // softmax in double in the reference's order (refSoftmax.h:23-50)
+    const double m = (double)__shfl_sync(0xffffffffu, myv, 0);
+    const double ex = (lane < K) ? exp((double)myv - m) : 0.0;
+    double sum = 1.0;
+    for (int j = 1; j < K; ++j) sum += __shfl_sync(0xffffffffu, ex, j);
+    if (lane < K) {
+      const float w = (float)(ex / sum);
+      const int owner = myi / p.El, le = myi - owner * p.El;
+      const uint32_t pos = atom_add<S>(&p.peers[owner].expert_cnt[le], 1u);
+      if (pos >= (uint32_t)p.cap_rows) {
+        raise_error(p, sc, FDMOE_ERR_ROW_OVERFLOW, (uint32_t)myi);
+      } else {
+        const size_t rowg = (size_t)le * p.cap_rows + pos;
+        sc.fix_row[half][lane] = (int32_t)rowg;
+        sc.fix_owner[half][lane] = owner;
+        p.topk_idx[(size_t)tok * K + lane] = myi;
+        p.topk_w[(size_t)tok * K + lane] = w;
+        p.dest_row[(size_t)tok * K + lane] = (int32_t)rowg;
+        *reinterpret_cast<uint4*>(&p.peers[owner].meta[rowg]) =
+            make_uint4(tok, (uint32_t)((p.rank << 8) | lane), __float_as_uint(w), 0u);
+      }
+    }
+  }
+  epi_bar();
+  prof_mark(p, sc, etid, 32);
+  if (live && !sc.abort) {
+    // the four warps of a half copy the staged row to its K destinations
+    for (int k = (ewarp & 3); k < K; k += 4) {
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.peers[sc.fix_owner[half][k]].packed) +
+                                            (size_t)sc.fix_row[half][k] * H);
+      for (int v = lane; v < H / 8; v += 32) dst[v] = sc.xrow[half][v];
+    }
+  }
+  ptx::fence_proxy_async();  // packed rows are read by TMA
+  epi_bar();
+  prof_mark(p, sc, etid, 33);
+  const uint32_t ntok = (tok_b != 0xffffffffu) ? 2u : 1u;
+  if (p.eager && !sc.abort && (uint32_t)etid < ntok * (uint32_t)K) {
+    const int hf = etid / K, k = etid % K;
+    const int rowg = sc.fix_row[hf][k], owner = sc.fix_owner[hf][k];
+    const uint32_t le = (uint32_t)rowg / (uint32_t)p.cap_rows, pos = (uint32_t)rowg % (uint32_t)p.cap_rows;
+    const uint32_t j = pos / 128u, nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
+    fence_acqrel<S>();
+    const uint32_t prev = atom_add<S>(&p.peers[owner].tile_landed[(size_t)le * p.MT + j], 1u);
+    if (prev + 1u == 128u) {
+      fence_acqrel<S>();
+      queue_push<S>(p, p.peers[owner], nt1, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
+        a = task_word(FDMOE_TASK_FFN1, le, i);
+        b = j;
+        c = 128u;
+      });
+    }
+  }
+  if (p.eager) epi_bar();
+  if (etid == 0) {
+    fence_acqrel<S>();
+    const uint32_t done = atomicAdd(&p.peers[p.rank].ctl->pack_done, ntok) + ntok;
     if (done == (uint32_t)p.T) gate_phase_finished<S>(p);
   }
+  return true;
 }
 
 // ============================================================ FLUSH and FFN
@@ -702,55 +785,67 @@ template <bool S>
 __device__ __noinline__ void flush_task(const FdmoeParams& p, SmemCtl& sc, int etid) {
   const FdmoePeer& me = p.peers[p.rank];
   const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
-  fence_acqrel<S>();
+  const int lane = etid & 31, w = etid >> 5;
+  // (the FLUSH task was taken from the queue with an acquire load that is ordered after every
+  // rank's row reservations, so the counts below are final)
+  // per-expert task and tile counts, then an exclusive prefix over the experts
+  // (shuffle scan inside each of the four warps that hold experts, warp totals
+  // through shared memory)
+  uint32_t full = 0, rem = 0, ntask = 0, ntile = 0;
   if (etid < p.El) {
     const uint32_t cnt = ld_relaxed<S>(&me.expert_cnt[etid]);
-    const uint32_t full = cnt / 128u, rem = cnt % 128u;
-    sc.full_tiles[etid] = full;
-    sc.rem_rows[etid] = rem;
-    sc.pre[etid + 1] = p.eager ? (rem ? nt1 : 0u) : (full + (rem ? 1u : 0u)) * nt1;
+    full = cnt / 128u;
+    rem = cnt % 128u;
+    ntile = full + (rem ? 1u : 0u);
+    ntask = p.eager ? (rem ? nt1 : 0u) : ntile * nt1;
+  }
+  uint32_t inc_task = ntask, inc_tile = ntile;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t a = __shfl_up_sync(0xffffffffu, inc_task, off);
+    const uint32_t b = __shfl_up_sync(0xffffffffu, inc_tile, off);
+    if (lane >= off) {
+      inc_task += a;
+      inc_tile += b;
+    }
+  }
+  if (lane == 31 && w < 4) {
+    sc.pre[w] = inc_task;
+    sc.pre[8 + w] = inc_tile;
   }
   epi_bar();
+  uint32_t off_task = 0, total = 0, mt = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (i < w) off_task += sc.pre[i];
+    total += sc.pre[i];
+    mt += sc.pre[8 + i];
+  }
   if (etid == 0) {
-    sc.pre[0] = 0;
-    uint32_t mt = 0;
-    for (int e = 0; e < p.El; ++e) {
-      sc.pre[e + 1] += sc.pre[e];
-      mt += sc.full_tiles[e] + (sc.rem_rows[e] ? 1u : 0u);
-    }
-    const uint32_t total = sc.pre[p.El];
-    sc.q_total = total;
     sc.q_t0 = total ? atom_add<false>(&me.ctl->q_head, total) : 0u;
     st_relaxed<false>(&me.ctl->mtiles_total, mt);
   }
   epi_bar();
-  const uint32_t total = sc.q_total, t0 = sc.q_t0;
-  for (uint32_t idx = etid; idx < total; idx += kEpiThreads) {
-    int lo = 0, hi = p.El;  // largest e with pre[e] <= idx
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (sc.pre[mid] <= idx) lo = mid; else hi = mid;
-    }
-    const uint32_t e = (uint32_t)lo, r = idx - sc.pre[lo];
-    const uint32_t full = sc.full_tiles[e], rem = sc.rem_rows[e];
+  const uint32_t t0 = sc.q_t0;
+  const uint32_t first = off_task + inc_task - ntask;  // exclusive prefix of this expert
+  for (uint32_t r = 0; r < ntask; ++r) {
     uint32_t j, n, rows;
     if (p.eager) {
       j = full; n = r; rows = rem;
     } else {
       j = r / nt1; n = r - j * nt1; rows = (j < full) ? 128u : rem;
     }
-    FdmoeSlot* s = &me.slots[(t0 + idx) & (uint32_t)p.queue_mask];
-    s->a = task_word(FDMOE_TASK_FFN1, e, n);
+    FdmoeSlot* s = &me.slots[(t0 + first + r) & (uint32_t)p.queue_mask];
+    s->a = task_word(FDMOE_TASK_FFN1, (uint32_t)etid, n);
     s->b = j;
     s->c = rows;
   }
   // one fence orders every payload above before every sequence word below
   fence_acqrel<false>();
-  for (uint32_t idx = etid; idx < total; idx += kEpiThreads)
-    st_relaxed<false>(&me.slots[(t0 + idx) & (uint32_t)p.queue_mask].seq, t0 + idx + 1u);
+  for (uint32_t r = 0; r < ntask; ++r)
+    st_relaxed<false>(&me.slots[(t0 + first + r) & (uint32_t)p.queue_mask].seq, t0 + first + r + 1u);
   epi_bar();
   if (etid == 0) {
-    fence_acqrel<false>();
     st_release<false>(&me.ctl->flush_done, 1u);
     maybe_close(p);
   }
@@ -855,55 +950,10 @@ __device__ __forceinline__ void ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc,
   }
 }
 
-// COMBINE: out[t, :] = sum over slots k = 0..K-1 (in that order, fp32) of
-// y[t, k, :], for the tokens of one group.  One warp per token; the K loads of
-// a 16-byte column vector are issued together, then summed in slot order.
-__device__ __noinline__ void combine_task(const FdmoeParams& p, int ewarp, int lane, uint32_t g) {
-  const int t_begin = (int)g * p.combine_group;
-  const int t_end = min(t_begin + p.combine_group, p.T);
-  const bf16* ys = reinterpret_cast<const bf16*>(p.peers[p.rank].ystage);
-  bf16* out = reinterpret_cast<bf16*>(p.out);
-  const int nvec = p.H / 8, K = p.K;
-  for (int t = t_begin + ewarp; t < t_end; t += kEpiThreads / 32) {
-    const bf16* yt = ys + (size_t)t * K * p.H;
-    for (int v = lane; v < nvec; v += 64) {
-      const bool two = v + 32 < nvec;
-      uint4 r0[FDMOE_MAX_TOPK], r1[FDMOE_MAX_TOPK];
-#pragma unroll
-      for (int k = 0; k < FDMOE_MAX_TOPK; ++k) {
-        if (k < K) {
-          r0[k] = ld_cg_u4(yt + (size_t)k * p.H + v * 8);
-          if (two) r1[k] = ld_cg_u4(yt + (size_t)k * p.H + (v + 32) * 8);
-        }
-      }
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        if (half == 1 && !two) break;
-        float acc[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-#pragma unroll
-        for (int k = 0; k < FDMOE_MAX_TOPK; ++k) {
-          if (k < K) {
-            const uint4 r = half ? r1[k] : r0[k];
-            const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              acc[2 * i] += bf16_lo(w[i]);
-              acc[2 * i + 1] += bf16_hi(w[i]);
-            }
-          }
-        }
-        uint4 o;
-        o.x = pack_bf16(acc[0], acc[1]);
-        o.y = pack_bf16(acc[2], acc[3]);
-        o.z = pack_bf16(acc[4], acc[5]);
-        o.w = pack_bf16(acc[6], acc[7]);
-        *reinterpret_cast<uint4*>(out + (size_t)t * p.H + (v + half * 32) * 8) = o;
-      }
-    }
-  }
-}
+// COMBINE streams the K weighted rows of each token of a group through the
+// shared-memory stage ring with 1-D bulk copies (issued by the TMA warp) in
+// pieces of up to 2048 columns: stage layout [K][piece], 4 KB per slot row.
+constexpr int kCombineCols = 2048;
 
 template <bool S>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -930,6 +980,10 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
     for (int r = 0; r < kRing; ++r) {
       ptx::mbar_init(&sc.ring_full[r], 1);
       ptx::mbar_init(&sc.ring_empty[r], 2 + kEpiThreads / 32);
+    }
+    for (int d = 0; d < kDone; ++d) {
+      ptx::mbar_init(&sc.done_full[d], 1);
+      ptx::mbar_init(&sc.done_empty[d], 1);
     }
     sc.abort = 0;
     sc.flag = 0;
@@ -1005,7 +1059,14 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         const FdmoeSlot t = queue_pop<S>(p, sc);
         sc.ring[r] = t;
         ptx::mbar_arrive(&sc.ring_full[r]);
-        if ((t.a & 0xffu) == FDMOE_TASK_EXIT) break;
+        const uint32_t kind = t.a & 0xffu;
+        if (kind == FDMOE_TASK_EXIT) break;
+        if (kind != FDMOE_TASK_FFN1 && kind != FDMOE_TASK_FFN2 && kind != FDMOE_TASK_COMBINE) {
+          // Only tile tasks (and COMBINE, whose rows are prefetched by bulk copies) profit from being queued behind one another (their loads and
+          // MMAs run ahead of the epilogue).  Behind a long task of another kind a claimed
+          // ticket would just sit here while other workers idle: wait until it is done.
+          if (!wait_bar(p, sc, &sc.ring_empty[r], ph, FDMOE_ERR_TIMEOUT_RING)) break;
+        }
       }
     }
     __syncwarp();
@@ -1043,10 +1104,46 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
               const int32_t brow = (int32_t)(e * 2u * (uint32_t)p.I + n * FDMOE_TILE_N1);
               ptx::tma_load_2d(sb, &p.tm_w13, &sc.full_bar[s], kx, brow);
               ptx::tma_load_2d(sb + kStageA, &p.tm_w13, &sc.full_bar[s], kx, brow + p.I);
+              // The weights come from HBM: ask L2 for them kPrefetch k-blocks ahead, so that the
+              // shared-memory stages only have to cover the L2 latency.
+              if (kb + kPrefetch < nkb) {
+                ptx::tma_prefetch_l2_2d(&p.tm_w13, kx + kPrefetch * FDMOE_TILE_K, brow);
+                ptx::tma_prefetch_l2_2d(&p.tm_w13, kx + kPrefetch * FDMOE_TILE_K, brow + p.I);
+              }
             } else {
               ptx::tma_load_2d(sa, &p.tm_act, &sc.full_bar[s], kx, arow);
               const int32_t brow = (int32_t)(e * (uint32_t)p.H + n * FDMOE_TILE_N2);
               ptx::tma_load_2d(sb, &p.tm_w2, &sc.full_bar[s], kx, brow);
+              if (kb + kPrefetch < nkb) ptx::tma_prefetch_l2_2d(&p.tm_w2, kx + kPrefetch * FDMOE_TILE_K, brow);
+            }
+          }
+          if (!ok) break;
+        } else if (kind == FDMOE_TASK_GATEFIX) {
+          bool ok = true;
+          for (uint32_t kb = 0; kb < nkb1; ++kb, ++stage_it) {
+            const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
+            ok = wait_bar(p, sc, &sc.empty_bar[s], sph ^ 1u, FDMOE_ERR_TIMEOUT_STAGE);
+            if (!ok) break;
+            ptx::mbar_expect_tx(&sc.full_bar[s], (uint32_t)min(128, p.E) * FDMOE_TILE_K * 2u);
+            ptx::tma_load_2d(stage + s * kStageBytes, &p.tm_gate, &sc.full_bar[s], (int32_t)(kb * FDMOE_TILE_K), 0);
+          }
+          if (!ok) break;
+        } else if (kind == FDMOE_TASK_COMBINE) {
+          const int t_begin = (int)t.b * p.combine_group, t_end = min(t_begin + p.combine_group, p.T);
+          const bf16* ys = reinterpret_cast<const bf16*>(me.ystage);
+          ptx::fence_proxy_async();  // the rows were written with generic stores
+          bool ok = true;
+          for (int tk = t_begin; tk < t_end && ok; ++tk) {
+            for (int c0 = 0; c0 < p.H; c0 += kCombineCols, ++stage_it) {
+              const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
+              ok = wait_bar(p, sc, &sc.empty_bar[s], sph ^ 1u, FDMOE_ERR_TIMEOUT_STAGE);
+              if (!ok) break;
+              const uint32_t wbytes = (uint32_t)min(kCombineCols, p.H - c0) * 2u;
+              uint8_t* sa = stage + s * kStageBytes;
+              ptx::mbar_expect_tx(&sc.full_bar[s], wbytes * (uint32_t)p.K);
+              for (int k = 0; k < p.K; ++k)
+                ptx::bulk_load_1d(sa + k * (kCombineCols * 2), ys + ((size_t)tk * p.K + k) * p.H + c0, wbytes,
+                                  &sc.full_bar[s]);
             }
           }
           if (!ok) break;
@@ -1092,6 +1189,12 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           }
           if (!ok) break;
           ptx::umma_commit(&sc.tmem_full[acc]);
+        } else if (kind == FDMOE_TASK_GATEFIX) {
+          stage_it += nkb1;  // consumed by the epilogue warps
+        } else if (kind == FDMOE_TASK_COMBINE) {
+          // the stages of this task are consumed by the epilogue warps: keep the count in step
+          const int t_begin = (int)t.b * p.combine_group, t_end = min(t_begin + p.combine_group, p.T);
+          stage_it += (uint32_t)((t_end - t_begin) * ((p.H + kCombineCols - 1) / kCombineCols));
         }
         ptx::mbar_arrive(&sc.ring_empty[r]);
       }
@@ -1100,7 +1203,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
   } else if (warp >= kWarpEpi0) {
     const int etid = tid - kWarpEpi0 * 32, ewarp = warp - kWarpEpi0;
     const int q = warp & 3, h = ewarp >> 2;
-    uint32_t tile_it = 0;
+    uint32_t tile_it = 0, done_it = 0, stage_it = 0;
     for (uint32_t it = 0;; ++it) {
       const uint32_t r = it % kRing, ph = (it / kRing) & 1u;
       // the group leaves together: a lone warp breaking out would strand the
@@ -1115,15 +1218,19 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       if (kind == FDMOE_TASK_GATE) {
         const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
         ++tile_it;
+        stage_it += nkb1;
         if (!epi_vote_all(wait_bar(p, sc, &sc.tmem_full[acc], aph, FDMOE_ERR_TIMEOUT_TMEM))) break;
         if (p.prof && etid == 0) pt1 = prof_now();
         ptx::tcgen05_fence_after();
         gate_epilogue<S>(p, sc, tmem_base + acc * kAccCols, &sc.tmem_empty[acc], q, h, lane, etid, ewarp, j);
       } else if (kind == FDMOE_TASK_PACK) {
         pack_task<S>(p, sc, etid, ewarp, lane, j, rows);
+      } else if (kind == FDMOE_TASK_GATEFIX) {
+        if (!gatefix_task<S>(p, sc, stage, stage_it, etid, ewarp, lane, j, rows)) break;
       } else if (kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2) {
         const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
         ++tile_it;
+        stage_it += (kind == FDMOE_TASK_FFN1) ? nkb1 : nkb2;
         if (!epi_vote_all(wait_bar(p, sc, &sc.tmem_full[acc], aph, FDMOE_ERR_TIMEOUT_TMEM))) break;
         if (p.prof && etid == 0) pt1 = prof_now();
         ptx::tcgen05_fence_after();
@@ -1137,74 +1244,61 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         if (lane == 0) ptx::mbar_arrive(&sc.tmem_empty[acc]);
         const uint32_t pta = (p.prof && etid == 0) ? prof_now() : 0u;
 
-        if (kind == FDMOE_TASK_FFN1) {
-          if (!(p.debug_flags & 4)) ptx::fence_proxy_async();  // the activation tile is read by TMA in FFN2
-          prof_mark(p, sc, etid, 20);
-          epi_bar();
-          prof_mark(p, sc, etid, 21);
-          if (etid == 0 && p.mode != 2) {
-            if (!(p.debug_flags & 2)) fence_acqrel<false>();
-            prof_mark(p, sc, etid, 22);
-            const uint32_t prev = atomicAdd(&p.ffn1_done[(size_t)e * p.MT + j], 1u);
-            prof_mark(p, sc, etid, 23);
-            if (prev == nt1 - 1u) {
-              if (!(p.debug_flags & 2)) fence_acqrel<false>();
-              queue_push<false>(p, me, nt2, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
-                a = task_word(FDMOE_TASK_FFN2, e, i);
-                b = j;
-                c = rows;
-              });
-            }
-          }
-        } else {
-          epi_bar();
-          if (etid == 0) {
-            int last = 0;
-            if (p.mode != 2) {
-              if (!(p.debug_flags & 2)) fence_acqrel<S>();
-              const uint32_t prev = atomicAdd(&p.ffn2_done[(size_t)e * p.MT + j], 1u);
-              if (!(p.debug_flags & 2)) fence_acqrel<S>();
-              last = prev == nt2 - 1u;
-            }
-            sc.flag = last;
-          }
-          epi_bar();
-          if (sc.flag) {
-            // every hidden-column tile of this m-tile is stored: tell the home ranks
-            if ((uint32_t)etid < rows) {
-              const uint4 mraw = ld_cg_u4(&me.meta[(size_t)e * p.cap_rows + (size_t)j * 128 + etid]);
-              const int token = (int)mraw.x, home = (int)mraw.y >> 8;
-              const uint32_t g = (uint32_t)(token / p.combine_group);
-              const FdmoePeer& hp = p.peers[home];
-              fence_acqrel<S>();
-              const uint32_t prev = atom_add<S>(&hp.tok_arrivals[g], 1u);
-              const int th = (home == p.rank) ? p.T : (int)ld_relaxed<S>(&hp.ctl->tokens_launch);
-              const int gt = min(p.combine_group, th - (int)g * p.combine_group);
-              if (prev + 1u == (uint32_t)(gt * p.K)) {
-                fence_acqrel<S>();
-                queue_push<S>(p, hp, 1u, [&](uint32_t, uint32_t& a, uint32_t& b, uint32_t& c) {
-                  a = FDMOE_TASK_COMBINE;
-                  b = g;
-                  c = 0;
-                });
-              }
-            }
-            epi_bar();
-            if (etid == 0) {
-              atomicAdd(&ctl->mtiles_done, 1u);
-              maybe_close(p);
-            }
-          }
-        }
-        if (etid == 0) prof_event(p, sc, kind + 16u, pt1, pta, prof_now());
-      } else if (kind == FDMOE_TASK_COMBINE) {
-        combine_task(p, ewarp, lane, j);
+        // The tile's stores are issued.  Dependency counting, successor pushes and
+        // the notifications of the home ranks are done by the completion warp, off
+        // the epilogue's critical path.
+        // activations are read by TMA in FFN2, weighted rows by bulk copies in COMBINE
+        if (!(p.debug_flags & 4)) ptx::fence_proxy_async();
         epi_bar();
         if (etid == 0 && p.mode != 2) {
-          const int t_begin = (int)j * p.combine_group;
-          const int cnt = min(p.combine_group, p.T - t_begin);
+          const uint32_t d = done_it % kDone, dph = (done_it / kDone) & 1u;
+          if (wait_bar(p, sc, &sc.done_empty[d], dph ^ 1u, FDMOE_ERR_TIMEOUT_RING)) {
+            sc.done_ring[d] = t;
+            ptx::mbar_arrive(&sc.done_full[d]);
+          }
+        }
+        ++done_it;
+        if (etid == 0) prof_event(p, sc, kind + 16u, pt1, pta, prof_now());
+      } else if (kind == FDMOE_TASK_COMBINE) {
+        // out[t, :] = sum over slots k = 0..K-1 (in that order, fp32) of y[t, k, :]
+        const int t_begin = (int)j * p.combine_group, t_end = min(t_begin + p.combine_group, p.T);
+        bf16* outp = reinterpret_cast<bf16*>(p.out);
+        bool ok = true;
+        for (int tk = t_begin; tk < t_end && ok; ++tk) {
+          for (int c0 = 0; c0 < p.H; c0 += kCombineCols, ++stage_it) {
+            const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
+            ok = epi_vote_all(wait_bar(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE));
+            if (!ok) break;
+            const int nvec = min(kCombineCols, p.H - c0) / 8;
+            if (etid < nvec) {
+              const uint4* sm = reinterpret_cast<const uint4*>(stage + s * kStageBytes) + etid;
+              float acc[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+              for (int k = 0; k < p.K; ++k) {
+                const uint4 rr = sm[k * (kCombineCols / 8)];
+                const uint32_t w[4] = {rr.x, rr.y, rr.z, rr.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  acc[2 * i] += bf16_lo(w[i]);
+                  acc[2 * i + 1] += bf16_hi(w[i]);
+                }
+              }
+              uint4 o;
+              o.x = pack_bf16(acc[0], acc[1]);
+              o.y = pack_bf16(acc[2], acc[3]);
+              o.z = pack_bf16(acc[4], acc[5]);
+              o.w = pack_bf16(acc[6], acc[7]);
+              *reinterpret_cast<uint4*>(outp + (size_t)tk * p.H + c0 + etid * 8) = o;
+            }
+            epi_bar();  // every thread has read the stage
+            if (etid == 0) ptx::mbar_arrive(&sc.empty_bar[s]);
+          }
+        }
+        if (!ok) break;
+        if (etid == 0 && p.mode != 2) {
           fence_acqrel<false>();
-          atomicAdd(&ctl->tokens_combined, (uint32_t)cnt);
+          atomicAdd(&ctl->tokens_combined, (uint32_t)(t_end - t_begin));
           maybe_close(p);
         }
       } else if (kind == FDMOE_TASK_FLUSH) {
@@ -1241,6 +1335,79 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&sc.ring_empty[r]);
     }
+    if (etid == 0 && p.mode != 2) {
+      // tell the completion warp that nothing more will come
+      const uint32_t d = done_it % kDone, dph = (done_it / kDone) & 1u;
+      if (wait_bar(p, sc, &sc.done_empty[d], dph ^ 1u, FDMOE_ERR_TIMEOUT_RING)) {
+        sc.done_ring[d].a = FDMOE_TASK_EXIT;
+        ptx::mbar_arrive(&sc.done_full[d]);
+      }
+    }
+  } else if (warp == kWarpTmem && p.mode != 2) {
+    // ---- completion warp: per finished tile, count it and publish what it unblocks
+    for (uint32_t it = 0;; ++it) {
+      const uint32_t d = it % kDone, dph = (it / kDone) & 1u;
+      int ok = 1;
+      if (lane == 0) ok = wait_bar(p, sc, &sc.done_full[d], dph, FDMOE_ERR_TIMEOUT_RING) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      const FdmoeSlot t = sc.done_ring[d];
+      const uint32_t kind = t.a & 0xffu;
+      if (kind == FDMOE_TASK_EXIT) break;
+      const uint32_t e = (t.a >> 8) & 0xfffu, j = t.b, rows = t.c;
+      if (kind == FDMOE_TASK_FFN1) {
+        if (lane == 0) {
+          if (!(p.debug_flags & 2)) fence_acqrel<false>();
+          const uint32_t prev = atomicAdd(&p.ffn1_done[(size_t)e * p.MT + j], 1u);
+          if (prev == nt1 - 1u) {
+            if (!(p.debug_flags & 2)) fence_acqrel<false>();
+            queue_push<false>(p, me, nt2, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
+              a = task_word(FDMOE_TASK_FFN2, e, i);
+              b = j;
+              c = rows;
+            });
+          }
+        }
+      } else {
+        int last = 0;
+        if (lane == 0) {
+          if (!(p.debug_flags & 2)) fence_acqrel<S>();
+          const uint32_t prev = atomicAdd(&p.ffn2_done[(size_t)e * p.MT + j], 1u);
+          if (!(p.debug_flags & 2)) fence_acqrel<S>();
+          last = prev == nt2 - 1u;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          // every hidden-column tile of this m-tile is stored: tell the home ranks
+          for (uint32_t r = lane; r < rows; r += 32) {
+            const uint4 mraw = ld_cg_u4(&me.meta[(size_t)e * p.cap_rows + (size_t)j * 128 + r]);
+            const int token = (int)mraw.x, home = (int)mraw.y >> 8;
+            const uint32_t g = (uint32_t)(token / p.combine_group);
+            const FdmoePeer& hp = p.peers[home];
+            fence_acqrel<S>();
+            const uint32_t prev = atom_add<S>(&hp.tok_arrivals[g], 1u);
+            const int th = (home == p.rank) ? p.T : (int)ld_relaxed<S>(&hp.ctl->tokens_launch);
+            const int gt = min(p.combine_group, th - (int)g * p.combine_group);
+            if (prev + 1u == (uint32_t)(gt * p.K)) {
+              fence_acqrel<S>();
+              queue_push<S>(p, hp, 1u, [&](uint32_t, uint32_t& a, uint32_t& b, uint32_t& c) {
+                a = FDMOE_TASK_COMBINE;
+                b = g;
+                c = 0;
+              });
+            }
+          }
+          __syncwarp();
+          if (lane == 0) {
+            atomicAdd(&ctl->mtiles_done, 1u);
+            maybe_close(p);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&sc.done_empty[d]);
+    }
+    __syncwarp();
   }
 
   // ---- teardown

@@ -11,6 +11,7 @@ enum {
   FDMOE_MAX_WORLD = 8,
   FDMOE_MAX_TOPK = 8,
   FDMOE_MAX_EXPERTS = 128,
+  FDMOE_MAX_HIDDEN = 4096,  // a token row is staged in shared memory by the exact gate path
   FDMOE_TILE_M = 128,    // rows of one expert's packed buffer per GEMM tile
   FDMOE_TILE_N1 = 128,   // FFN1: activation columns per tile (MMA N = 2 * 128: gate + up)
   FDMOE_TILE_N2 = 256,   // FFN2: hidden columns per tile
@@ -31,6 +32,7 @@ enum {
   FDMOE_TASK_EXIT = 7,
   FDMOE_TASK_GATE = 8,     // (token tile): gate GEMM, top-k, softmax, row reservation
   FDMOE_TASK_PACK = 9,     // (first token, count): copy token rows into the owners' expert buffers
+  FDMOE_TASK_GATEFIX = 10, // (token, token): exact fp32 gate of nearly tied tokens, then their pack
 };
 
 // Status codes written by the kernel (first error wins).
@@ -144,6 +146,7 @@ typedef struct {
   int32_t* topk_idx;    // [max_tokens, K]
   float* topk_w;        // [max_tokens, K]
   int32_t* dest_row;    // [max_tokens, K] row of (token, slot) in its owner's expert buffers
+  uint8_t* tok_flag;    // [max_tokens] 1 = token is handled by a GATEFIX task, not by PACK
   uint32_t* ffn1_done;  // [El * MT]
   uint32_t* ffn2_done;  // [El * MT]
   uint32_t* status_host;  // mapped pinned word: first error code, readable without a sync
