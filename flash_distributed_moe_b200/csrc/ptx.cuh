@@ -1,7 +1,6 @@
-// Inline-PTX wrappers for sm_100a: mbarrier, TMA (cp.async.bulk.tensor, no
-// multicast anywhere), tcgen05 (TMEM alloc, MMA, commit, ld), proxy fences and
-// scoped acquire/release accesses.  Every wait helper here is bounded: it
-// returns false when its budget runs out instead of spinning forever.
+// Inline-PTX wrappers for sm_100a: mbarrier, TMA loads (tiled and 1-D bulk; every
+// load targets the issuing CTA's own shared memory only), tcgen05 (TMEM alloc,
+// MMA, commit, ld), proxy fences and scoped acquire/release accesses.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
