@@ -189,6 +189,7 @@ class MoeKernelLauncher final : public moe::IMoeKernelLauncher {
   // host-buffer entry point staging
   void *host_in_dev_ = nullptr, *host_out_dev_ = nullptr;
   uint32_t* prof_ = nullptr;  // optional event trace (FLASHMOE_PROFILE=1)
+  uint32_t* stuck_ = nullptr;  // per CTA and warp: where a role gave up waiting
   float* debug_logits_ = nullptr;  // optional gate-logit dump (FLASHMOE_DEBUG_LOGITS=1)
   EncodeTiledFn encode_ = nullptr;
   Bootstrap boot_;
@@ -200,7 +201,7 @@ void MoeKernelLauncher::FreeAll() {
     if (r != rank_ && peer_bases_[r]) cudaIpcCloseMemHandle(peer_bases_[r]);
   peer_bases_.clear();
   void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, dest_row_, tok_flag_, gate_bf16_, w13_bf16_, w2_bf16_,
-                  tok_bf16_, out_bf16_, host_in_dev_, host_out_dev_, prof_, debug_logits_};
+                  tok_bf16_, out_bf16_, host_in_dev_, host_out_dev_, prof_, debug_logits_, stuck_};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   arena_ = nullptr;
@@ -212,6 +213,7 @@ void MoeKernelLauncher::FreeAll() {
   gate_bf16_ = w13_bf16_ = w2_bf16_ = tok_bf16_ = out_bf16_ = host_in_dev_ = host_out_dev_ = nullptr;
   prof_ = nullptr;
   debug_logits_ = nullptr;
+  stuck_ = nullptr;
   if (status_host_) cudaFreeHost(status_host_);
   status_host_ = nullptr;
   boot_.Close();
@@ -401,7 +403,10 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   params_.MT = g_.MT;
   params_.queue_mask = (int32_t)(g_.queue_cap - 1);
   params_.combine_group = g_.combine_group;
-  params_.eager = EnvInt("FLASHMOE_EAGER", world > 1 ? 1 : 0);
+  // Publishing full tiles as they land starts expert work earlier, but scatters an expert's
+  // tiles in time, so its weights are re-read from HBM; at the benchmark sizes publishing
+  // everything at the flush, ordered by expert, is faster.  FLASHMOE_EAGER=1 selects the former.
+  params_.eager = EnvInt("FLASHMOE_EAGER", 0);
   params_.debug_flags = EnvInt("FLASHMOE_DEBUG_FLAGS", 0);
   params_.timeout_ns = (uint64_t)std::max(1, EnvInt("FLASHMOE_TIMEOUT_MS", 2000)) * 1000000ull;
   params_.gate_w = gate_dev;
@@ -413,6 +418,12 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   params_.ffn1_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn1_done);
   params_.ffn2_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn2_done);
   params_.status_host = status_dev_;
+  {
+    const size_t bytes = (size_t)grid_ * 16 * 16;
+    CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&stuck_), bytes));
+    CUDA_ERROR_CHECK(cudaMemsetAsync(stuck_, 0, bytes, stream));
+    params_.stuck = stuck_;
+  }
   if (EnvInt("FLASHMOE_DEBUG_LOGITS", 0)) {
     CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&debug_logits_), std::max<size_t>(4, (size_t)maxTokens * 128 * 4)));
     params_.debug_logits = debug_logits_;
@@ -515,6 +526,7 @@ cudaError_t MoeKernelLauncher::DebugRead(int which, void* dst, size_t offset, si
       memcpy(dst, info, std::min(bytes, sizeof(info)));
       return cudaSuccess;
     case 9: src = debug_logits_; size = debug_logits_ ? (size_t)g_.max_tokens_local * 128 * 4 : 0; break;
+    case 10: src = stuck_; size = (size_t)grid_ * 16 * 16; break;
     case 8: src = prof_; size = prof_ ? (size_t)grid_ * FDMOE_PROF_EVENTS * 16 : 0; break;
     default: return cudaErrorInvalidValue;
   }

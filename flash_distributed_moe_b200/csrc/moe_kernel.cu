@@ -63,6 +63,7 @@ struct __align__(16) SmemCtl {
   FdmoeSlot done_ring[kDone];
   uint32_t tmem_base;
   volatile uint32_t abort;
+  volatile uint32_t skip_done;  // COMBINE / GATEFIX tasks finished by the epilogue warps
   int32_t flag;
   uint32_t q_t0;
   uint32_t q_total;
@@ -230,6 +231,20 @@ __device__ __noinline__ void raise_error(const FdmoeParams& p, SmemCtl& sc, uint
 
 // Bounded mbarrier wait.  Returns false (after raising the error) on timeout
 // or when another role of this CTA has aborted.
+// Where a role gave up waiting (diagnostics, one record per CTA and warp):
+// {error code, byte offset of the barrier inside SmemCtl, parity, microseconds waited}.
+__device__ __noinline__ void record_stuck(const FdmoeParams& p, SmemCtl& sc, uint64_t* bar, uint32_t parity,
+                                          uint32_t err_code, uint64_t waited_ns) {
+  if (!p.stuck) return;
+  uint32_t* r = p.stuck + ((size_t)blockIdx.x * 16 + (threadIdx.x >> 5)) * 4;
+  r[0] = err_code;
+  r[1] = (uint32_t)(reinterpret_cast<uint8_t*>(bar) - reinterpret_cast<uint8_t*>(&sc));
+  r[2] = parity;
+  r[3] = (uint32_t)(waited_ns / 1000ull);
+}
+
+// Bounded mbarrier wait.  Returns false (after raising the error) on timeout
+// or when another role of this CTA has aborted.
 __device__ __forceinline__ bool wait_bar(const FdmoeParams& p, SmemCtl& sc, uint64_t* bar,
                                          uint32_t parity, uint32_t err_code) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
@@ -237,11 +252,29 @@ __device__ __forceinline__ bool wait_bar(const FdmoeParams& p, SmemCtl& sc, uint
   uint32_t spins = 0;
   while (!ptx::mbar_try_wait(bar, parity)) {
     if ((++spins & 63u) == 0u) {
-      if (sc.abort) return false;
-      if (ptx::globaltimer_ns() - t0 > p.timeout_ns) {
+      const uint64_t waited = ptx::globaltimer_ns() - t0;
+      if (sc.abort) {
+        record_stuck(p, sc, bar, parity, err_code | 0x100u, waited);
+        return false;
+      }
+      if (waited > p.timeout_ns) {
+        record_stuck(p, sc, bar, parity, err_code, waited);
         raise_error(p, sc, err_code, (blockIdx.x << 8) | (threadIdx.x >> 5));
         return false;
       }
+    }
+  }
+  return true;
+}
+
+// Same wait without raising an error: one budget's worth of polling.
+__device__ __forceinline__ bool wait_idle(const FdmoeParams& p, SmemCtl& sc, uint64_t* bar, uint32_t parity) {
+  const uint64_t t0 = ptx::globaltimer_ns();
+  uint32_t spins = 0;
+  while (!ptx::mbar_try_wait(bar, parity)) {
+    if ((++spins & 63u) == 0u) {
+      if (sc.abort || ptx::globaltimer_ns() - t0 > p.timeout_ns) return false;
+      __nanosleep(200);
     }
   }
   return true;
@@ -986,6 +1019,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       ptx::mbar_init(&sc.done_empty[d], 1);
     }
     sc.abort = 0;
+    sc.skip_done = 0;
     sc.flag = 0;
     sc.prof_n = 0;
     ptx::fence_mbar_init();
@@ -1156,7 +1190,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
     if (lane == 0) {
       constexpr uint32_t idesc256 = ptx::make_idesc_bf16(128, 256);
       constexpr uint32_t idesc128 = ptx::make_idesc_bf16(128, 128);
-      uint32_t stage_it = 0, tile_it = 0;
+      uint32_t stage_it = 0, tile_it = 0, skips = 0;
       for (uint32_t it = 0;; ++it) {
         const uint32_t r = it % kRing, ph = (it / kRing) & 1u;
         if (!wait_bar(p, sc, &sc.ring_full[r], ph, FDMOE_ERR_TIMEOUT_RING)) break;
@@ -1189,12 +1223,33 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           }
           if (!ok) break;
           ptx::umma_commit(&sc.tmem_full[acc]);
-        } else if (kind == FDMOE_TASK_GATEFIX) {
-          stage_it += nkb1;  // consumed by the epilogue warps
-        } else if (kind == FDMOE_TASK_COMBINE) {
-          // the stages of this task are consumed by the epilogue warps: keep the count in step
-          const int t_begin = (int)t.b * p.combine_group, t_end = min(t_begin + p.combine_group, p.T);
-          stage_it += (uint32_t)((t_end - t_begin) * ((p.H + kCombineCols - 1) / kCombineCols));
+        } else if (kind == FDMOE_TASK_GATEFIX || kind == FDMOE_TASK_COMBINE) {
+          // The stages of these tasks are consumed by the epilogue warps.  This warp must not
+          // run ahead of them: a stage barrier only tells phases apart by parity, so a waiter
+          // more than one phase ahead would take an old completion for its own.  Wait until
+          // the epilogue has finished the task, then step over its stages.
+          ++skips;
+          const uint64_t t0w = ptx::globaltimer_ns();
+          uint32_t spins = 0;
+          bool ok = true;
+          while (sc.skip_done < skips) {
+            if ((++spins & 63u) == 0u) {
+              if (sc.abort) { ok = false; break; }
+              if (ptx::globaltimer_ns() - t0w > 4ull * p.timeout_ns) {
+                raise_error(p, sc, FDMOE_ERR_TIMEOUT_STAGE, (blockIdx.x << 8) | 2u);
+                ok = false;
+                break;
+              }
+              __nanosleep(100);
+            }
+          }
+          if (!ok) break;
+          if (kind == FDMOE_TASK_GATEFIX) {
+            stage_it += nkb1;
+          } else {
+            const int t_begin = (int)t.b * p.combine_group, t_end = min(t_begin + p.combine_group, p.T);
+            stage_it += (uint32_t)((t_end - t_begin) * ((p.H + kCombineCols - 1) / kCombineCols));
+          }
         }
         ptx::mbar_arrive(&sc.ring_empty[r]);
       }
@@ -1227,6 +1282,10 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         pack_task<S>(p, sc, etid, ewarp, lane, j, rows);
       } else if (kind == FDMOE_TASK_GATEFIX) {
         if (!gatefix_task<S>(p, sc, stage, stage_it, etid, ewarp, lane, j, rows)) break;
+        if (etid == 0) {
+          __threadfence_block();
+          sc.skip_done = sc.skip_done + 1u;
+        }
       } else if (kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2) {
         const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
         ++tile_it;
@@ -1296,6 +1355,10 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           }
         }
         if (!ok) break;
+        if (etid == 0) {
+          __threadfence_block();
+          sc.skip_done = sc.skip_done + 1u;
+        }
         if (etid == 0 && p.mode != 2) {
           fence_acqrel<false>();
           atomicAdd(&ctl->tokens_combined, (uint32_t)(t_end - t_begin));
@@ -1348,7 +1411,14 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
     for (uint32_t it = 0;; ++it) {
       const uint32_t d = it % kDone, dph = (it / kDone) & 1u;
       int ok = 1;
-      if (lane == 0) ok = wait_bar(p, sc, &sc.done_full[d], dph, FDMOE_ERR_TIMEOUT_RING) ? 1 : 0;
+      if (lane == 0) {
+        // This warp may legitimately idle for a whole launch, so its own budget is four
+        // times the others': whoever actually stalls reports first.
+        ok = 0;
+        for (int tries = 0; tries < 4 && !ok && !sc.abort; ++tries)
+          ok = wait_idle(p, sc, &sc.done_full[d], dph) ? 1 : 0;
+        if (!ok && !sc.abort) raise_error(p, sc, FDMOE_ERR_TIMEOUT_RING, (blockIdx.x << 8) | 3u);
+      }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
       const FdmoeSlot t = sc.done_ring[d];

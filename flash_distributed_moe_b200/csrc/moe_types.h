@@ -152,6 +152,7 @@ typedef struct {
   uint32_t* status_host;  // mapped pinned word: first error code, readable without a sync
   int32_t* test_buf;    // task-system self test payload
   float* debug_logits;  // optional dump of the tensor-core gate logits [T, 128] (NULL = off)
+  uint32_t* stuck;      // [grid][16 warps][4] where each role gave up waiting (diagnostics)
   uint32_t* prof;       // optional event trace, FDMOE_PROF_EVENTS x 4 words per CTA (NULL = off)
 } FdmoeParams;
 
