@@ -19,8 +19,10 @@
 #include "../../include/flashmoe_c.h"
 #include "../../include/iMoeKernelLauncher.h"
 #include "bootstrap.h"
+#include "host_layout.h"
 #include "moe_types.h"
 
+#undef MOE_ERROR_LOG
 #define MOE_ERROR_LOG(...)                                   \
   do {                                                       \
     fprintf(stderr, "[MOE ERROR: %s:%d] ", __FILE__, __LINE__); \
@@ -45,97 +47,6 @@ IMoeKernelLauncher::~IMoeKernelLauncher() {}
 
 namespace fdmoe {
 namespace {
-
-size_t AlignUp(size_t v, size_t a) { return (v + a - 1) / a * a; }
-
-uint32_t NextPow2(uint64_t v) {
-  uint32_t p = 1;
-  while (p < v) p <<= 1;
-  return p;
-}
-
-// Offsets of every region inside a rank's symmetric arena.  Identical on all
-// ranks, so a peer's regions are found from its base pointer alone.
-struct ArenaLayout {
-  size_t ctl = 0;
-  size_t expert_cnt = 0, tile_landed = 0, tok_arrivals = 0, ffn1_done = 0, ffn2_done = 0;
-  size_t zero_begin = 0, zero_end = 0;  // per-launch reset range
-  size_t slots = 0, meta = 0, ystage = 0, packed = 0;
-  size_t total = 0;
-};
-
-struct Geometry {
-  int H = 0, I = 0, E = 0, K = 0, El = 0, world = 1;
-  int max_tokens_local = 0;  // this rank
-  int max_tokens_max = 0;    // largest over ranks (sizes token-indexed regions)
-  int64_t max_tokens_sum = 0;  // all ranks (sizes expert buffers)
-  int cap_rows = 0, MT = 0, combine_group = 16, groups = 0;
-  uint32_t queue_cap = 0;
-};
-
-ArenaLayout MakeLayout(const Geometry& g) {
-  ArenaLayout L;
-  size_t off = 0;
-  L.ctl = off;
-  off += AlignUp(sizeof(FdmoeCtl), 128);
-  L.zero_begin = L.ctl + offsetof(FdmoeCtl, launch_begin);
-  L.expert_cnt = off;
-  off += AlignUp((size_t)g.El * 4, 128);
-  L.tile_landed = off;
-  off += AlignUp((size_t)g.El * g.MT * 4, 128);
-  L.tok_arrivals = off;
-  off += AlignUp((size_t)g.groups * 4, 128);
-  L.ffn1_done = off;
-  off += AlignUp((size_t)g.El * g.MT * 4, 128);
-  L.ffn2_done = off;
-  off += AlignUp((size_t)g.El * g.MT * 4, 128);
-  L.zero_end = off;
-  L.slots = off;
-  off += AlignUp((size_t)g.queue_cap * sizeof(FdmoeSlot), 1024);
-  L.meta = off;
-  off += AlignUp((size_t)g.El * g.cap_rows * sizeof(FdmoeRowMeta), 1024);
-  L.ystage = off;
-  off += AlignUp((size_t)g.max_tokens_max * g.K * g.H * 2, 1024);
-  L.packed = off;
-  off += AlignUp((size_t)g.El * g.cap_rows * g.H * 2, 1024);
-  L.total = off;
-  return L;
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-EncodeTiledFn GetEncodeTiled() {
-  void* fn = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
-      qres != cudaDriverEntryPointSuccess)
-    return nullptr;
-  return reinterpret_cast<EncodeTiledFn>(fn);
-}
-
-// Row-major bf16 matrix [rows, cols]; one TMA box is 64 columns (128 bytes, the
-// swizzle span) by box_rows rows.
-cudaError_t MakeTensorMap(EncodeTiledFn enc, FdmoeTensorMap* out, const void* base, uint64_t rows,
-                          uint64_t cols, uint32_t box_rows) {
-  static_assert(sizeof(CUtensorMap) == sizeof(FdmoeTensorMap), "tensor map size");
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 2};
-  const cuuint32_t box[2] = {FDMOE_TILE_K, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    MOE_ERROR_LOG("cuTensorMapEncodeTiled failed with %d (rows %llu cols %llu)", (int)r,
-                  (unsigned long long)rows, (unsigned long long)cols);
-    return cudaErrorInvalidValue;
-  }
-  return cudaSuccess;
-}
 
 int EnvInt(const char* name, int dflt) {
   const char* v = getenv(name);

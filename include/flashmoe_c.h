@@ -82,6 +82,20 @@ int FlashMoeTestTaskSystem(FlashMoeHandle h, int32_t* data, int n, void* stream)
 int FlashMoeTestQueueGemm(FlashMoeHandle h, const uint32_t* rowsPerExpertHost, const void* A,
                           void* out, void* stream);
 
+/* The whole layer in one call that allocates nothing (no counterpart in the reference, whose
+ * launcher always allocates its scratch in Init, src/hip/launcher/moeKernelLauncher.hip:139-165).
+ * For callers that may not touch the device allocator: an engine that has frozen its memory pool,
+ * a callback that must not call allocating runtime functions, a process whose memory belongs to
+ * another allocator.  All scratch comes from a fixed 32 MiB array inside the library image (held
+ * on every GPU that loads the library); a call whose scratch does not fit is rejected with
+ * cudaErrorInvalidValue.  Single rank, bf16, device pointers; config == NULL selects the
+ * Qwen3-30B-A3B shape.  The first call on a device does one-time set-up and should be made
+ * outside of stream capture.  Calls share the array: do not let two of them overlap on a GPU.
+ * Returns after the layer has finished; a device-side error is reported as cudaErrorUnknown. */
+int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1ExpertWeights,
+                          const void* ffn2ExpertWeights, const void* tokens, void* output, int tokensNum,
+                          const FlashMoeConfig* config, void* stream);
+
 const char* FlashMoeErrorString(int code);
 
 #ifdef __cplusplus
