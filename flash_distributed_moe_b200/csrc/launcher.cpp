@@ -317,6 +317,7 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   // Publishing full tiles as they land starts expert work earlier, but scatters an expert's
   // tiles in time, so its weights are re-read from HBM; at the benchmark sizes publishing
   // everything at the flush, ordered by expert, is faster.  FLASHMOE_EAGER=1 selects the former.
+  params_.gate_rows = 128;
   params_.eager = EnvInt("FLASHMOE_EAGER", 0);
   params_.debug_flags = EnvInt("FLASHMOE_DEBUG_FLAGS", 0);
   params_.timeout_ns = (uint64_t)std::max(1, EnvInt("FLASHMOE_TIMEOUT_MS", 2000)) * 1000000ull;
@@ -377,7 +378,15 @@ cudaError_t MoeKernelLauncher::LaunchBf16(const void* tokens, void* output, int 
   FdmoeParams p = params_;
   if (tokensNum > 0 && mode == 0) {
     // the token matrix moves between launches: its TMA descriptor is rebuilt (host-only arithmetic)
-    CUDA_ERROR_CHECK(MakeTensorMap(encode_, &p.tm_x, tokens, (uint64_t)tokensNum, g_.H, std::min(128, tokensNum)));
+    // GATE tile height: the smallest of 32/64/128 tokens that still gives every SM at most one tile,
+    // so that the gate phase spreads over as many SMs as possible
+    int rows = 128;
+    if (tokensNum <= 32 * grid_) rows = 32;
+    else if (tokensNum <= 64 * grid_) rows = 64;
+    p.gate_rows = EnvInt("FLASHMOE_GATE_ROWS", rows);
+    if (p.gate_rows != 32 && p.gate_rows != 64 && p.gate_rows != 128) p.gate_rows = rows;
+    CUDA_ERROR_CHECK(MakeTensorMap(encode_, &p.tm_x, tokens, (uint64_t)tokensNum, g_.H,
+                                   std::min(p.gate_rows, tokensNum)));
   }
   p.T = tokensNum;
   p.x = tokens;

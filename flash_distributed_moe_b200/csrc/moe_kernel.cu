@@ -45,6 +45,7 @@ constexpr int kStageA = FDMOE_TILE_M * FDMOE_TILE_K * 2;  // 16 KB
 constexpr int kStageB = 256 * FDMOE_TILE_K * 2;           // 32 KB
 constexpr int kStageBytes = kStageA + kStageB;            // 48 KB
 constexpr int kRing = 3;
+constexpr int kFixBlocks = 3;  // k-blocks of gate weights per stage in a GATEFIX task (3 x 16 KB)
 constexpr int kPrefetch = 8;  // k-blocks by which the L2 prefetch of weights runs ahead
 constexpr int kDone = 4;  // depth of the hand-off ring to the completion warp
 constexpr int kTmemCols = 512;
@@ -294,8 +295,11 @@ __device__ __forceinline__ void queue_push(const FdmoeParams& p, const FdmoePeer
     s->a = a;
     s->b = b;
     s->c = c;
-    st_release<S>(&s->seq, t0 + i + 1u);
   }
+  // one fence orders every payload (and whatever the caller wrote before) ahead of the
+  // sequence words; a release store per slot would pay for a fence each time
+  fence_acqrel<S>();
+  for (uint32_t i = 0; i < n; ++i) st_relaxed<S>(&q.slots[(t0 + i) & (uint32_t)p.queue_mask].seq, t0 + i + 1u);
 }
 
 __device__ __forceinline__ uint32_t task_word(uint32_t kind, uint32_t e, uint32_t n) {
@@ -476,9 +480,10 @@ template <bool S>
 __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, uint64_t* tmem_empty_bar,
                                            int q, int h, int lane, int etid, int ewarp, uint32_t tile) {
   const int E = p.E, K = p.K;
-  const int t0 = (int)tile * FDMOE_GATE_TOKENS;
-  const int nt = min(FDMOE_GATE_TOKENS, p.T - t0);
+  const int t0 = (int)tile * p.gate_rows;
+  const int nt = min(p.gate_rows, p.T - t0);
   const int kk = min(E, 9);
+  const int npass = p.gate_rows / 32;
 
   if (etid < 128) sc.cnt[etid] = 0;
   if (etid == 0) sc.n_flagged = 0;
@@ -486,7 +491,13 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
   // quadrant spill its 32 rows to shared memory, then every warp extracts the
   // top-9 of four rows with warp-wide arg-max rounds
   prof_mark(p, sc, etid, 40);
-  for (int pass = 0; pass < 4; ++pass) {
+  if (q >= npass) {
+    // this warp's TMEM lanes hold no token of the tile: it only has to release the accumulator
+    ptx::tcgen05_fence_before();
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(tmem_empty_bar);
+  }
+  for (int pass = 0; pass < npass; ++pass) {
     if (q == pass) {
       uint32_t v[32];
       const uint32_t tb = taddr + ((uint32_t)(q * 32) << 16) + h * 64;
@@ -712,27 +723,30 @@ __device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uin
   prof_mark(p, sc, etid, 30);
   // Exact logits: fp32 FMAs with k strictly ascending per output (bf16 x bf16
   // products are exact in fp32, so this equals the reference's `acc += a*b` bit
-  // for bit; reference refGemm.h:16-27).  The gate weights arrive 64 columns at a
-  // time through the stage ring (TMA, 128-byte swizzle: 16-byte chunk c of row r
+  // for bit; reference refGemm.h:16-27).  The gate weights arrive up to 192 columns
+  // (three 64-column boxes) per stage through the stage ring (TMA, 128-byte swizzle: 16-byte chunk c of row r
   // sits at chunk c ^ (r & 7)); the token row is broadcast from shared memory.
   {
     float acc = 0.f;
     const uint32_t nkb = (uint32_t)(H / FDMOE_TILE_K);
-    for (uint32_t kb = 0; kb < nkb; ++kb, ++stage_it) {
+    for (uint32_t kb = 0; kb < nkb; kb += kFixBlocks, ++stage_it) {
       const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
       if (!epi_vote_all(wait_bar(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE))) return false;
       if (live && e < E) {
-        const uint4* tile = reinterpret_cast<const uint4*>(stage + s * kStageBytes);
+        const uint32_t nb = min((uint32_t)kFixBlocks, nkb - kb);
+        for (uint32_t i = 0; i < nb; ++i) {
+          const uint4* tile = reinterpret_cast<const uint4*>(stage + s * kStageBytes + i * kStageA);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 wv = tile[e * 8 + (c ^ (e & 7))];
-          const uint4 xv = sc.xrow[half][kb * 8 + c];
-          const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-          const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+          for (int c = 0; c < 8; ++c) {
+            const uint4 wv = tile[e * 8 + (c ^ (e & 7))];
+            const uint4 xv = sc.xrow[half][(kb + i) * 8 + c];
+            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            acc = fmaf(bf16_lo(xw[j]), bf16_lo(ww[j]), acc);
-            acc = fmaf(bf16_hi(xw[j]), bf16_hi(ww[j]), acc);
+            for (int j = 0; j < 4; ++j) {
+              acc = fmaf(bf16_lo(xw[j]), bf16_lo(ww[j]), acc);
+              acc = fmaf(bf16_hi(xw[j]), bf16_hi(ww[j]), acc);
+            }
           }
         }
       }
@@ -1063,16 +1077,18 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
     __syncthreads();
   }
 
-  // ---- seed the queue: one GATE task per 128-token tile (nothing to gate: the
-  // rank's "gate phase" is finished at once, it may still serve its peers)
-  if (p.mode != 2 && !sc.abort && blockIdx.x == 0 && tid == 0) {
-    const uint32_t n_tiles = (uint32_t)((p.T + FDMOE_GATE_TOKENS - 1) / FDMOE_GATE_TOKENS);
+  // ---- seed the queue: every CTA publishes its share of the GATE tasks (tile b, b + grid, ...),
+  // so that all tiles are available at once.  Nothing to gate: the rank's "gate phase" is
+  // finished at once (it may still serve its peers).
+  if (p.mode != 2 && !sc.abort && tid == 0) {
+    const uint32_t n_tiles = (uint32_t)((p.T + p.gate_rows - 1) / p.gate_rows);
     if (n_tiles == 0) {
-      gate_phase_finished<S>(p);
-    } else {
-      queue_push<false>(p, me, n_tiles, [](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
+      if (blockIdx.x == 0) gate_phase_finished<S>(p);
+    } else if (blockIdx.x < n_tiles) {
+      const uint32_t mine = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+      queue_push<false>(p, me, mine, [](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
         a = FDMOE_TASK_GATE;
-        b = i;
+        b = blockIdx.x + i * gridDim.x;
         c = 0;
       });
     }
@@ -1117,9 +1133,9 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           const uint32_t e = (t.a >> 8) & 0xfffu, n = t.a >> 20, j = t.b;
           const bool f1 = kind == FDMOE_TASK_FFN1, gt = kind == FDMOE_TASK_GATE;
           const uint32_t nkb = (f1 || gt) ? nkb1 : nkb2;
-          const int32_t arow = gt ? (int32_t)(j * FDMOE_GATE_TOKENS) : (int32_t)(e * (uint32_t)p.cap_rows + j * 128u);
+          const int32_t arow = gt ? (int32_t)(j * (uint32_t)p.gate_rows) : (int32_t)(e * (uint32_t)p.cap_rows + j * 128u);
           // bytes one GATE stage receives: both boxes are clamped to the tensor extents
-          const uint32_t gate_bytes = (uint32_t)(min(128, p.T) + min(128, p.E)) * FDMOE_TILE_K * 2u;
+          const uint32_t gate_bytes = (uint32_t)(min(p.gate_rows, p.T) + min(128, p.E)) * FDMOE_TILE_K * 2u;
           ptx::fence_proxy_async();  // rows / activations were written with generic stores
           bool ok = true;
           for (uint32_t kb = 0; kb < nkb && ok; ++kb, ++stage_it) {
@@ -1128,6 +1144,10 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
             if (!ok) break;
             uint8_t* sa = stage + s * kStageBytes;
             uint8_t* sb = sa + kStageA;
+            if ((p.debug_flags & 8) && !gt) {  // timing experiment: tiles computed from stale operands
+              ptx::mbar_arrive(&sc.full_bar[s]);
+              continue;
+            }
             ptx::mbar_expect_tx(&sc.full_bar[s], gt ? gate_bytes : (uint32_t)kStageBytes);
             const int32_t kx = (int32_t)(kb * FDMOE_TILE_K);
             if (gt) {
@@ -1154,12 +1174,16 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           if (!ok) break;
         } else if (kind == FDMOE_TASK_GATEFIX) {
           bool ok = true;
-          for (uint32_t kb = 0; kb < nkb1; ++kb, ++stage_it) {
+          for (uint32_t kb = 0; kb < nkb1; kb += kFixBlocks, ++stage_it) {
             const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
             ok = wait_bar(p, sc, &sc.empty_bar[s], sph ^ 1u, FDMOE_ERR_TIMEOUT_STAGE);
             if (!ok) break;
-            ptx::mbar_expect_tx(&sc.full_bar[s], (uint32_t)min(128, p.E) * FDMOE_TILE_K * 2u);
-            ptx::tma_load_2d(stage + s * kStageBytes, &p.tm_gate, &sc.full_bar[s], (int32_t)(kb * FDMOE_TILE_K), 0);
+            const uint32_t nb = min((uint32_t)kFixBlocks, nkb1 - kb);
+            const uint32_t blk_bytes = (uint32_t)min(128, p.E) * FDMOE_TILE_K * 2u;
+            ptx::mbar_expect_tx(&sc.full_bar[s], nb * blk_bytes);
+            for (uint32_t i = 0; i < nb; ++i)
+              ptx::tma_load_2d(stage + s * kStageBytes + i * kStageA, &p.tm_gate, &sc.full_bar[s],
+                               (int32_t)((kb + i) * FDMOE_TILE_K), 0);
           }
           if (!ok) break;
         } else if (kind == FDMOE_TASK_COMBINE) {
@@ -1245,7 +1269,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           }
           if (!ok) break;
           if (kind == FDMOE_TASK_GATEFIX) {
-            stage_it += nkb1;
+            stage_it += (nkb1 + kFixBlocks - 1) / kFixBlocks;
           } else {
             const int t_begin = (int)t.b * p.combine_group, t_end = min(t_begin + p.combine_group, p.T);
             stage_it += (uint32_t)((t_end - t_begin) * ((p.H + kCombineCols - 1) / kCombineCols));

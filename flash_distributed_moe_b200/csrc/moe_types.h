@@ -17,7 +17,7 @@ enum {
   FDMOE_TILE_N2 = 256,   // FFN2: hidden columns per tile
   FDMOE_TILE_K = 64,     // one 128-byte swizzle atom of bf16 per stage
   FDMOE_GATE_TOKENS = 128,  // tokens per gate tile (one tcgen05 M tile)
-  FDMOE_PACK_TOKENS = 16,   // tokens per PACK task
+  FDMOE_PACK_TOKENS = 8,    // tokens per PACK task (one per epilogue warp)
 };
 
 // Task kinds held by the global work queue.
@@ -131,10 +131,11 @@ typedef struct {
   int32_t MT;           // cap_rows / 128
   int32_t queue_mask;   // capacity - 1 (capacity is a power of two)
   int32_t combine_group;  // tokens per COMBINE task
+  int32_t gate_rows;    // tokens per GATE task: 32, 64 or 128 (rows of the 128-row MMA tile that are used)
   int32_t eager;        // publish full tiles as they land instead of at flush
   int32_t mode;         // 0 full layer; 2 static tasks only (no gate)
   int32_t debug_flags;  // timing experiments only (results become invalid): 1 skip FFN stores,
-                        // 2 skip completion fences, 4 skip proxy fences
+                        // 2 skip completion fences, 4 skip proxy fences, 8 skip the operand loads of FFN tiles
   uint32_t expected_static;  // mode 2: tasks pre-filled by the host
   uint32_t epoch;       // launch counter (identical on all ranks)
   uint64_t timeout_ns;  // budget of every device-side wait
