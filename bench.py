@@ -39,6 +39,20 @@ def flops_per_token(s) -> float:
     return 2.0 * s.hidden * s.experts + s.topk * 6.0 * s.hidden * s.inter
 
 
+def algorithmic_bytes(s, tokens, world) -> float:
+    """HBM bytes one launch has to move on one GPU: active expert weights once, token rows in, packed rows
+    written and read, activations written and read, weighted rows written and read, output rows out, gate."""
+    pairs = tokens * s.topk
+    weights = (s.experts // world) * 3 * s.hidden * s.inter * 2
+    return (weights + 2 * s.hidden * s.experts + 2 * s.hidden * tokens * 2
+            + 2 * (2 * s.hidden * pairs) + 2 * (2 * s.inter * pairs) + 2 * (2 * s.hidden * pairs))
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the persistent kernel from ncu, for the
+# workloads that were captured (profiles/moe_persistent_kernel_dram_traffic_qwen3-30b_4096tok.md)
+MEASURED_TRAFFIC = {("30b", 4096, 1): 1.68e9 + 332.5e6}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -304,9 +318,8 @@ def main():
         value = tokens_total / (ms_per_step * 1e-3)
         flop_launch = flops_per_token(shape) * T  # per GPU under uniform routing
         achieved_tflops = flop_launch / (mean_launch_ms * 1e-3) / 1e12
-        weight_bytes = (shape.experts // world) * 3 * shape.hidden * shape.inter * 2
-        act_bytes = T * shape.hidden * 2 * (2 + 2 * shape.topk * 2) + T * shape.topk * shape.inter * 2 * 2
-        hbm_gbs = (weight_bytes + act_bytes) / (mean_launch_ms * 1e-3) / 1e9
+        alg_bytes = algorithmic_bytes(shape, T, world)
+        hbm_gbs = alg_bytes / (mean_launch_ms * 1e-3) / 1e9
         result = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -316,7 +329,9 @@ def main():
                        "hidden": shape.hidden, "inter": shape.inter, "tokens_per_gpu": T,
                        "l2_policy": "inputs larger than L2 (expert weights read per step exceed 126 MB)"},
             "roofline": {"bound": "tensor", "achieved": achieved_tflops, "peak": peaks["bf16_tflops"],
-                         "unit": "TFLOP/s", "frac": achieved_tflops / peaks["bf16_tflops"], "traffic": None,
+                         "unit": "TFLOP/s", "frac": achieved_tflops / peaks["bf16_tflops"],
+                         "traffic": MEASURED_TRAFFIC.get((args.shape, T, world)), "traffic_unit": "bytes/launch (ncu dram read+write)",
+                         "algorithmic_bytes": alg_bytes,
                          "peak_source": peaks["source"] + " burst",
                          "kernel": "moe_persistent_kernel", "kernel_ms": mean_launch_ms,
                          "hbm_algorithmic_gbs": hbm_gbs, "hbm_frac_of_" + peaks["source"]: hbm_gbs / peaks["hbm_gbs"]},

@@ -216,8 +216,11 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   {
     const uint64_t rows_max = std::min<uint64_t>((uint64_t)g_.max_tokens_sum * g_.K, (uint64_t)g_.El * g_.cap_rows);
     const uint64_t mtiles = rows_max / FDMOE_TILE_M + g_.El;
+    // tile tasks + COMBINE groups + FLUSH + this rank's GATE (>= 32 tokens each), PACK (8 tokens each)
+    // and GATEFIX tasks (2 tokens each, every token in the worst case)
     const uint64_t tasks = mtiles * (g_.I / FDMOE_TILE_N1 + g_.H / FDMOE_TILE_N2) + g_.groups + 64 +
-                           (uint64_t)g_.max_tokens_max / 128 * 2 + 4096;
+                           (uint64_t)g_.max_tokens_max / 32 + (uint64_t)g_.max_tokens_max / FDMOE_PACK_TOKENS +
+                           (uint64_t)g_.max_tokens_max / 2 + 1024;
     g_.queue_cap = NextPow2(tasks + 4ull * grid_ + 1024);
   }
   layout_ = MakeLayout(g_);

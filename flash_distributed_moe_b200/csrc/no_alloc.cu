@@ -134,7 +134,8 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
     const uint64_t rows_max = std::min<uint64_t>((uint64_t)g.max_tokens_sum * g.K, (uint64_t)g.El * g.cap_rows);
     const uint64_t mtiles = rows_max / FDMOE_TILE_M + g.El;
     const uint64_t tasks = mtiles * (g.I / FDMOE_TILE_N1 + g.H / FDMOE_TILE_N2) + g.groups + 64 +
-                           (uint64_t)g.max_tokens_max / 128 * 2 + 1024;
+                           (uint64_t)g.max_tokens_max / 32 + (uint64_t)g.max_tokens_max / FDMOE_PACK_TOKENS +
+                           (uint64_t)g.max_tokens_max / 2 + 512;
     g.queue_cap = NextPow2(tasks + 4ull * d->grid + 256);
   }
   const ArenaLayout L = MakeLayout(g);

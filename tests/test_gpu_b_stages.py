@@ -97,3 +97,31 @@ def test_qwen3_30b_reference_test_stream_48_tokens_in_place():
     x, gate, w13, w2 = tl.reference_stream_inputs(48)
     check_layer(synth.QWEN3_30B_A3B, x, gate, w13, w2, max_tokens=50, golden="qwen3_30b_t48_refstream.npz",
                 inplace=True)
+
+
+def test_all_logits_tied_every_token_takes_the_exact_path():
+    # zero gate weights: every logit is 0, every token is a tie and is re-gated in the reference's fp32
+    # order; the reference keeps the lower expert index first (refTopk.h:36-58), so experts 0..K-1 win
+    s = synth.TINY
+    gate, w13, w2 = synth.make_weights(s, seed=2, std=0.05)
+    gate = torch.zeros_like(gate)
+    check_layer(s, synth.make_tokens(s, 150, seed=2), gate, w13, w2, max_tokens=150)
+
+
+def test_identical_tokens_one_hot_expert_set():
+    # every token is the same row: K experts receive every row (the per-expert buffer is filled to its
+    # capacity of one row per token), all other experts none
+    s = synth.TINY
+    gate, w13, w2 = synth.make_weights(s, seed=3, std=0.05)
+    x = synth.make_tokens(s, 1, seed=3).repeat(300, 1).contiguous()
+    check_layer(s, x, gate, w13, w2, max_tokens=300)
+
+
+def test_zipf_skewed_routing():
+    # expert popularity skewed by a per-expert gate bias injected through a constant activation column
+    # (the fourth benchmark configuration's construction), 700 tokens
+    s = synth.TINY
+    gate, w13, w2 = synth.make_weights(s, seed=4, std=0.05)
+    x = synth.make_tokens(s, 700, seed=4)
+    gate, x = synth.add_zipf_bias(s, gate, x, s=1.2, scale=1.0, seed=4)
+    check_layer(s, x, gate, w13, w2, max_tokens=700)
