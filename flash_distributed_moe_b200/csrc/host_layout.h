@@ -33,7 +33,7 @@ inline uint32_t NextPow2(uint64_t v) {
 // ranks, so a peer's regions are found from its base pointer alone.
 struct ArenaLayout {
   size_t ctl = 0;
-  size_t expert_cnt = 0, tile_landed = 0, tok_arrivals = 0, ffn1_done = 0, ffn2_done = 0;
+  size_t expert_cnt = 0, landed = 0, send_cnt = 0, tok_arrivals = 0, ffn1_done = 0, ffn2_done = 0;
   size_t zero_begin = 0, zero_end = 0;  // per-launch reset range
   size_t slots = 0, meta = 0, ystage = 0, packed = 0;
   size_t total = 0;
@@ -56,8 +56,10 @@ inline ArenaLayout MakeLayout(const Geometry& g) {
   L.zero_begin = L.ctl + offsetof(FdmoeCtl, launch_begin);
   L.expert_cnt = off;
   off += AlignUp((size_t)g.El * 4, 128);
-  L.tile_landed = off;
-  off += AlignUp((size_t)g.El * g.MT * 4, 128);
+  L.landed = off;
+  off += AlignUp((size_t)g.El * 4, 128);
+  L.send_cnt = off;
+  off += AlignUp((size_t)g.E * 4, 128);
   L.tok_arrivals = off;
   off += AlignUp((size_t)g.groups * 4, 128);
   L.ffn1_done = off;

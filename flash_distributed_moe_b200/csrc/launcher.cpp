@@ -90,8 +90,8 @@ class MoeKernelLauncher final : public moe::IMoeKernelLauncher {
   void* act_ = nullptr;
   int32_t* topk_idx_ = nullptr;
   float* topk_w_ = nullptr;
-  int32_t* dest_row_ = nullptr;
-  uint8_t* tok_flag_ = nullptr;
+  int32_t* send_src_ = nullptr;  // this rank's send lists [E][maxTokens]
+  int32_t* send_dst_ = nullptr;
   uint32_t* status_host_ = nullptr;
   uint32_t* status_dev_ = nullptr;
   // fp32 I/O mode: bf16 copies of the weights and token staging
@@ -111,7 +111,7 @@ void MoeKernelLauncher::FreeAll() {
   for (int r = 0; r < (int)peer_bases_.size(); ++r)
     if (r != rank_ && peer_bases_[r]) cudaIpcCloseMemHandle(peer_bases_[r]);
   peer_bases_.clear();
-  void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, dest_row_, tok_flag_, gate_bf16_, w13_bf16_, w2_bf16_,
+  void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, send_src_, send_dst_, gate_bf16_, w13_bf16_, w2_bf16_,
                   tok_bf16_, out_bf16_, host_in_dev_, host_out_dev_, prof_, debug_logits_, stuck_};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -119,8 +119,7 @@ void MoeKernelLauncher::FreeAll() {
   act_ = nullptr;
   topk_idx_ = nullptr;
   topk_w_ = nullptr;
-  dest_row_ = nullptr;
-  tok_flag_ = nullptr;
+  send_src_ = send_dst_ = nullptr;
   gate_bf16_ = w13_bf16_ = w2_bf16_ = tok_bf16_ = out_bf16_ = host_in_dev_ = host_out_dev_ = nullptr;
   prof_ = nullptr;
   debug_logits_ = nullptr;
@@ -216,10 +215,11 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   {
     const uint64_t rows_max = std::min<uint64_t>((uint64_t)g_.max_tokens_sum * g_.K, (uint64_t)g_.El * g_.cap_rows);
     const uint64_t mtiles = rows_max / FDMOE_TILE_M + g_.El;
-    // tile tasks + COMBINE groups + FLUSH + this rank's GATE (>= 32 tokens each), PACK (8 tokens each)
+    // tile tasks + COMBINE groups + GATED + this rank's GATE (>= 32 tokens each), PACK (64 rows each)
     // and GATEFIX tasks (2 tokens each, every token in the worst case)
     const uint64_t tasks = mtiles * (g_.I / FDMOE_TILE_N1 + g_.H / FDMOE_TILE_N2) + g_.groups + 64 +
-                           (uint64_t)g_.max_tokens_max / 32 + (uint64_t)g_.max_tokens_max / FDMOE_PACK_TOKENS +
+                           (uint64_t)g_.max_tokens_max / 32 +
+                           (uint64_t)g_.max_tokens_max * g_.K / FDMOE_PACK_ROWS + g_.E +
                            (uint64_t)g_.max_tokens_max / 2 + 1024;
     g_.queue_cap = NextPow2(tasks + 4ull * grid_ + 1024);
   }
@@ -231,8 +231,11 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   CUDA_ERROR_CHECK(cudaMalloc(&act_, (size_t)g_.El * g_.cap_rows * g_.I * 2));
   CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&topk_idx_), std::max<size_t>(4, (size_t)maxTokens * g_.K * 4)));
   CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&topk_w_), std::max<size_t>(4, (size_t)maxTokens * g_.K * 4)));
-  CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&dest_row_), std::max<size_t>(4, (size_t)maxTokens * g_.K * 4)));
-  CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&tok_flag_), std::max<size_t>(16, (size_t)maxTokens)));
+  {
+    const size_t list_bytes = std::max<size_t>(16, (size_t)g_.E * maxTokens * 4);
+    CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&send_src_), list_bytes));
+    CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&send_dst_), list_bytes));
+  }
   CUDA_ERROR_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped));
   memset(status_host_, 0, 64);
   CUDA_ERROR_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_), status_host_, 0));
@@ -300,7 +303,7 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
     pv.ctl = reinterpret_cast<FdmoeCtl*>(b + layout_.ctl);
     pv.slots = reinterpret_cast<FdmoeSlot*>(b + layout_.slots);
     pv.expert_cnt = reinterpret_cast<uint32_t*>(b + layout_.expert_cnt);
-    pv.tile_landed = reinterpret_cast<uint32_t*>(b + layout_.tile_landed);
+    pv.landed = reinterpret_cast<uint32_t*>(b + layout_.landed);
     pv.tok_arrivals = reinterpret_cast<uint32_t*>(b + layout_.tok_arrivals);
     pv.packed = b + layout_.packed;
     pv.meta = reinterpret_cast<FdmoeRowMeta*>(b + layout_.meta);
@@ -317,19 +320,17 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   params_.MT = g_.MT;
   params_.queue_mask = (int32_t)(g_.queue_cap - 1);
   params_.combine_group = g_.combine_group;
-  // Publishing full tiles as they land starts expert work earlier, but scatters an expert's
-  // tiles in time, so its weights are re-read from HBM; at the benchmark sizes publishing
-  // everything at the flush, ordered by expert, is faster.  FLASHMOE_EAGER=1 selects the former.
-  params_.gate_rows = 128;
-  params_.eager = EnvInt("FLASHMOE_EAGER", 0);
+  params_.gate_rows = 128;  // per launch: 32, 64 or 128 by token count
   params_.debug_flags = EnvInt("FLASHMOE_DEBUG_FLAGS", 0);
   params_.timeout_ns = (uint64_t)std::max(1, EnvInt("FLASHMOE_TIMEOUT_MS", 2000)) * 1000000ull;
   params_.gate_w = gate_dev;
   params_.act = act_;
   params_.topk_idx = topk_idx_;
   params_.topk_w = topk_w_;
-  params_.dest_row = dest_row_;
-  params_.tok_flag = tok_flag_;
+  params_.send_src = send_src_;
+  params_.send_dst = send_dst_;
+  params_.send_stride = std::max(maxTokens, 1);
+  params_.send_cnt = reinterpret_cast<uint32_t*>(arena_ + layout_.send_cnt);
   params_.ffn1_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn1_done);
   params_.ffn2_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn2_done);
   params_.status_host = status_dev_;

@@ -6,7 +6,9 @@
 //           reservation in the owners' expert buffers (tokens whose leading
 //           logits are nearly tied are recomputed with fp32 FMAs in the
 //           reference's accumulation order, so the selection is the reference's);
-//   PACK    16-token group: copies the token rows to their K destinations;
+//   GATED   all ranks have gated: publishes this rank's PACK tasks, expert by expert;
+//   PACK    64 rows of one expert: copies them into the owner's expert buffer; the
+//           sender that completes an expert publishes its FFN1 tiles;
 //   FFN1/2  128-row expert tiles on tcgen05 with TMEM accumulators fed by TMA
 //           (SwiGLU epilogue; routing-weight epilogue stored on the home rank);
 //   COMBINE token group: ordered sum of the K weighted rows.
@@ -79,6 +81,7 @@ struct __align__(16) SmemCtl {
       // GATE task scratch (per expert / per token of the tile)
       uint32_t cnt[128];
       uint32_t base[128];
+      uint32_t sbase[128];                      // first send-list entry of the tile per expert
       uint32_t flagged[FDMOE_GATE_TOKENS];
       uint8_t isflag[FDMOE_GATE_TOKENS];
       float logit_tile[32][132];                // one 32-token quarter of the logits (padded rows)
@@ -91,8 +94,6 @@ struct __align__(16) SmemCtl {
       // GATEFIX task scratch: two token rows and their exact logits
       uint4 xrow[2][FDMOE_MAX_HIDDEN / 8];
       float exact[2][128];
-      int32_t fix_row[2][FDMOE_MAX_TOPK];
-      int32_t fix_owner[2][FDMOE_MAX_TOPK];
     };
     // FFN epilogues: per-warp staging of a 32-row x 64-byte chunk (80-byte pitch
     // keeps the 16-byte accesses of a quarter warp on distinct banks)
@@ -351,17 +352,17 @@ __device__ __forceinline__ void maybe_close(const FdmoeParams& p) {
   st_release<false>(&ctl->closed, 1u);
 }
 
-// Every token of this rank is packed (all its rows are written and fenced):
-// tell every rank; whoever completes a rank's count asks it to flush.
+// The routing of every token of this rank is decided (rows reserved on their
+// owners, send lists complete): tell every rank; whoever completes a rank's
+// count hands it the GATED task, from which its row counts are final.
 template <bool S>
-__device__ void gate_phase_finished(const FdmoeParams& p) {
+__device__ void gating_finished(const FdmoeParams& p) {
   for (int q = 0; q < p.world; ++q) {
     fence_acqrel<S>();
-    const uint32_t prev = atom_add<S>(&p.peers[q].ctl->ranks_done, 1u);
+    const uint32_t prev = atom_add<S>(&p.peers[q].ctl->ranks_gated, 1u);
     if (prev == (uint32_t)p.world - 1u) {
-      fence_acqrel<S>();
       queue_push<S>(p, p.peers[q], 1u, [](uint32_t, uint32_t& a, uint32_t& b, uint32_t& c) {
-        a = FDMOE_TASK_FLUSH;
+        a = FDMOE_TASK_GATED;
         b = 0;
         c = 0;
       });
@@ -369,7 +370,14 @@ __device__ void gate_phase_finished(const FdmoeParams& p) {
   }
 }
 
-// ===================================================================== GATE
+// Counts `n` tokens of this rank as gated; the caller has written their send-list entries.
+template <bool S>
+__device__ __forceinline__ void count_gated(const FdmoeParams& p, uint32_t n) {
+  fence_acqrel<S>();
+  const uint32_t done = atomicAdd(&p.peers[p.rank].ctl->gated_tokens, n) + n;
+  if (n && done == (uint32_t)p.T) gating_finished<S>(p);
+}
+
 // Monotonic unsigned key of a float (larger float <=> larger key; -0 counts as +0).
 __device__ __forceinline__ uint32_t order_key(float f) {
   const uint32_t u = __float_as_uint(f + 0.0f);
@@ -543,7 +551,6 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
       const float tau = 6e-8f * (float)p.H * fmaxf(1.0f, fabsf(sc.top_v[etid][0]));
       for (int j = 0; j + 1 < kk; ++j) tie |= (sc.top_v[etid][j] - sc.top_v[etid][j + 1]) < tau;
       if (tie) sc.flagged[atomicAdd(&sc.n_flagged, 1u)] = (uint32_t)etid;
-      p.tok_flag[t0 + etid] = tie ? 1 : 0;
     }
     sc.isflag[etid] = tie ? 1 : 0;
   }
@@ -577,7 +584,8 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
   }
   epi_bar();
   prof_mark(p, sc, etid, 5);
-  // reserve rows in the owners' expert buffers: one atomic per expert and tile
+  // reserve rows in the owners' expert buffers and entries in this rank's send
+  // lists: one atomic each per expert and tile
   if (etid < E) {
     const uint32_t cnt = sc.cnt[etid];
     if (cnt) {
@@ -585,6 +593,7 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
       const uint32_t base = atom_add<S>(&p.peers[owner].expert_cnt[le], cnt);
       if (base + cnt > (uint32_t)p.cap_rows) raise_error(p, sc, FDMOE_ERR_ROW_OVERFLOW, etid);
       sc.base[etid] = base;
+      sc.sbase[etid] = atomicAdd(&p.send_cnt[etid], cnt);
     }
   }
   epi_bar();
@@ -594,7 +603,9 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
       const int e = sc.top_i[etid][k];
       const int owner = e / p.El, le = e - owner * p.El;
       const size_t rowg = (size_t)le * p.cap_rows + sc.base[e] + sc.lpos[etid][k];
-      p.dest_row[(size_t)(t0 + etid) * K + k] = (int32_t)rowg;
+      const size_t ent = (size_t)e * p.send_stride + sc.sbase[e] + sc.lpos[etid][k];
+      p.send_src[ent] = ((t0 + etid) << 4) | k;
+      p.send_dst[ent] = (int32_t)rowg;
       // FdmoeRowMeta {token, home << 8 | slot, weight, pad} as one 16-byte store
       *reinterpret_cast<uint4*>(&p.peers[owner].meta[rowg]) =
           make_uint4((uint32_t)(t0 + etid), (uint32_t)((p.rank << 8) | k), __float_as_uint(sc.tk_w[etid][k]), 0u);
@@ -603,110 +614,106 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
   epi_bar();
   prof_mark(p, sc, etid, 7);
   if (etid == 0 && !sc.abort) {
-    fence_acqrel<S>();
-    const uint32_t ngroups = (uint32_t)((nt + FDMOE_PACK_TOKENS - 1) / FDMOE_PACK_TOKENS);
     const uint32_t nf = sc.n_flagged, nfix = (nf + 1u) / 2u;
-    queue_push<false>(p, p.peers[p.rank], ngroups + nfix, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
-      if (i < nfix) {  // the slow tasks first
+    if (nfix) {
+      fence_acqrel<false>();
+      queue_push<false>(p, p.peers[p.rank], nfix, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
         a = FDMOE_TASK_GATEFIX;
         b = (uint32_t)t0 + sc.flagged[2 * i];
         c = (2 * i + 1 < nf) ? (uint32_t)t0 + sc.flagged[2 * i + 1] : 0xffffffffu;
-      } else {
-        const uint32_t g = i - nfix;
-        a = FDMOE_TASK_PACK;
-        b = (uint32_t)t0 + g * FDMOE_PACK_TOKENS;
-        c = (uint32_t)min(FDMOE_PACK_TOKENS, nt - (int)g * FDMOE_PACK_TOKENS);
-      }
-    });
+      });
+    }
+    count_gated<S>(p, (uint32_t)nt - nf);
   }
 }
 
 // ===================================================================== PACK
-// Copies `count` token rows to their K destinations each (local stores or
-// stores into a peer's expert buffer), one warp per token, then accounts for
-// them.  In eager mode the writer that completes a 128-row tile publishes its
-// FFN1 tasks on the owner's queue.
+// Sends `count` rows of one expert (entries [first, first + count) of this rank's
+// send list for it) to the expert's owner: one warp per row, 16-byte stores into
+// the owner's expert buffer (local or over NVLink).  The sender whose rows
+// complete the expert (all ranks have finished gating before any PACK task
+// exists, so the expert's row count is final) publishes all its FFN1 tile tasks
+// on the owner's queue, m-tile major, so that the tiles of one expert run
+// together and share its weights through L2.
 template <bool S>
-__device__ __noinline__ void pack_task(const FdmoeParams& p, SmemCtl& sc, int etid, int ewarp, int lane, uint32_t t_first,
-                          uint32_t count) {
-  const int H = p.H, K = p.K;
+__device__ __noinline__ void pack_task(const FdmoeParams& p, SmemCtl& sc, int etid, int ewarp, int lane, uint32_t e,
+                                       uint32_t first, uint32_t count) {
+  const int H = p.H;
   const bf16* x = reinterpret_cast<const bf16*>(p.x);
-  // a warp takes tokens ewarp and ewarp + 8 of the group and keeps the loads of both in flight
-  // (tokens handed to a GATEFIX task are packed there)
-  const bool has[2] = {(uint32_t)ewarp < count && !__ldcg(&p.tok_flag[t_first + ewarp]),
-                       (uint32_t)ewarp + 8u < count && !__ldcg(&p.tok_flag[t_first + ewarp + 8])};
-  // lane k < K keeps the destination of slot k of both tokens; broadcast by shuffle when needed
-  int my_row[2] = {0, 0}, my_owner[2] = {0, 0};
-  const uint4* src[2];
-#pragma unroll
-  for (int s2 = 0; s2 < 2; ++s2) {
-    const uint32_t t = t_first + (uint32_t)ewarp + 8u * s2;
-    src[s2] = reinterpret_cast<const uint4*>(x + (size_t)(has[s2] ? t : t_first) * H);
-    if (has[s2] && lane < K) {
-      my_row[s2] = __ldcg(&p.dest_row[(size_t)t * K + lane]);
-      my_owner[s2] = __ldcg(&p.topk_idx[(size_t)t * K + lane]) / p.El;
-    }
-  }
-  for (int vbase = 0; vbase < H / 8; vbase += 256) {
-    uint4 r[2][8];
-#pragma unroll
-    for (int s2 = 0; s2 < 2; ++s2) {
+  const int owner = (int)e / p.El, le = (int)e - owner * p.El;
+  const FdmoePeer& op = p.peers[owner];
+  bf16* packed = reinterpret_cast<bf16*>(op.packed);
+  const int32_t* src_list = p.send_src + (size_t)e * p.send_stride + first;
+  const int32_t* dst_list = p.send_dst + (size_t)e * p.send_stride + first;
+  // a warp takes rows ewarp, ewarp + 8, ... two at a time, so that the loads of both are in flight
+  for (uint32_t r0 = ewarp; r0 < count; r0 += 16) {
+    const bool has1 = r0 + 8 < count;
+    const int s0 = __ldcg(src_list + r0), d0 = __ldcg(dst_list + r0);
+    const int s1 = has1 ? __ldcg(src_list + r0 + 8) : s0, d1 = has1 ? __ldcg(dst_list + r0 + 8) : d0;
+    const uint4* src0 = reinterpret_cast<const uint4*>(x + (size_t)(s0 >> 4) * H);
+    const uint4* src1 = reinterpret_cast<const uint4*>(x + (size_t)(s1 >> 4) * H);
+    uint4* dst0 = reinterpret_cast<uint4*>(packed + (size_t)d0 * H);
+    uint4* dst1 = reinterpret_cast<uint4*>(packed + (size_t)d1 * H);
+    for (int vbase = 0; vbase < H / 8; vbase += 256) {
+      uint4 a[8], b[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int vi = vbase + lane + 32 * i;
-        r[s2][i] = (has[s2] && vi < H / 8) ? src[s2][vi] : make_uint4(0, 0, 0, 0);
+        a[i] = (vi < H / 8) ? src0[vi] : make_uint4(0, 0, 0, 0);
+        b[i] = (has1 && vi < H / 8) ? src1[vi] : make_uint4(0, 0, 0, 0);
       }
-    }
 #pragma unroll
-    for (int s2 = 0; s2 < 2; ++s2) {
-      for (int k = 0; k < K; ++k) {
-        const int row = __shfl_sync(0xffffffffu, my_row[s2], k);
-        const int owner = __shfl_sync(0xffffffffu, my_owner[s2], k);
-        if (!has[s2]) continue;
-        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.peers[owner].packed) + (size_t)row * H);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int vi = vbase + lane + 32 * i;
-          if (vi < H / 8) dst[vi] = r[s2][i];
+      for (int i = 0; i < 8; ++i) {
+        const int vi = vbase + lane + 32 * i;
+        if (vi < H / 8) {
+          dst0[vi] = a[i];
+          if (has1) dst1[vi] = b[i];
         }
       }
     }
   }
   ptx::fence_proxy_async();  // packed rows are read by TMA
   epi_bar();
-  if (p.eager && (uint32_t)etid < count * (uint32_t)K &&
-      !__ldcg(&p.tok_flag[t_first + (uint32_t)etid / (uint32_t)K])) {
-    const uint32_t t = t_first + (uint32_t)etid / (uint32_t)K, k = (uint32_t)etid % (uint32_t)K;
-    const int rowg = __ldcg(&p.dest_row[(size_t)t * K + k]);
-    const int owner = __ldcg(&p.topk_idx[(size_t)t * K + k]) / p.El;
-    const uint32_t le = (uint32_t)rowg / (uint32_t)p.cap_rows, pos = (uint32_t)rowg % (uint32_t)p.cap_rows;
-    const uint32_t j = pos / 128u, nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
+  if (etid == 0) {
     fence_acqrel<S>();
-    const uint32_t prev = atom_add<S>(&p.peers[owner].tile_landed[(size_t)le * p.MT + j], 1u);
-    if (prev + 1u == 128u) {
-      fence_acqrel<S>();
-      queue_push<S>(p, p.peers[owner], nt1, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
-        a = task_word(FDMOE_TASK_FFN1, le, i);
-        b = j;
-        c = 128u;
-      });
+    const uint32_t prev = atom_add<S>(&op.landed[le], count);
+    const uint32_t total = ld_relaxed<S>(&op.expert_cnt[le]);  // final: every rank has finished gating
+    sc.flag = (prev + count == total) ? (int)total : 0;
+    if (sc.flag) {
+      const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
+      const uint32_t ntask = ((total + 127u) / 128u) * nt1;
+      fence_acqrel<S>();  // the other senders' rows (observed through the counter) before the tasks
+      sc.q_t0 = atom_add<S>(&op.ctl->q_head, ntask);
     }
   }
-  if (p.eager) epi_bar();
-  if (etid == 0) {
-    uint32_t mine = 0;
-    for (uint32_t i = 0; i < count; ++i) mine += __ldcg(&p.tok_flag[t_first + i]) ? 0u : 1u;
-    fence_acqrel<S>();
-    const uint32_t done = atomicAdd(&p.peers[p.rank].ctl->pack_done, mine) + mine;
-    if (mine && done == (uint32_t)p.T) gate_phase_finished<S>(p);
+  epi_bar();
+  if (sc.flag) {
+    const uint32_t total = (uint32_t)sc.flag, nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
+    const uint32_t full = total / 128u, rem = total % 128u, ntask = ((total + 127u) / 128u) * nt1;
+    const uint32_t t0 = sc.q_t0;
+    bool any = false;
+    for (uint32_t idx = etid; idx < ntask; idx += kEpiThreads) {
+      const uint32_t j = idx / nt1, n = idx - j * nt1;
+      FdmoeSlot* sl = &op.slots[(t0 + idx) & (uint32_t)p.queue_mask];
+      sl->a = task_word(FDMOE_TASK_FFN1, (uint32_t)le, n);
+      sl->b = j;
+      sl->c = (j < full) ? 128u : rem;
+      any = true;
+    }
+    if (any) {
+      fence_acqrel<S>();
+      for (uint32_t idx = etid; idx < ntask; idx += kEpiThreads)
+        st_relaxed<S>(&op.slots[(t0 + idx) & (uint32_t)p.queue_mask].seq, t0 + idx + 1u);
+    }
   }
+  epi_bar();  // sc.flag / sc.q_t0 may be rewritten by the next task only after everyone has read them
 }
 
 // ================================================================== GATEFIX
 // Up to two tokens whose leading tensor-core logits were nearly tied: all E
 // logits are recomputed with fp32 FMAs in the reference's order (128 threads per
-// token, one expert each), then top-k, softmax, row reservation and the pack of
-// the token rows, i.e. everything GATE and PACK do for the other tokens.
+// token, one expert each), then top-k, softmax, row reservation and send-list
+// entries, i.e. everything GATE does for the other tokens.
 template <bool S>
 __device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uint8_t* stage, uint32_t& stage_it,
                                           int etid, int ewarp, int lane, uint32_t tok_a, uint32_t tok_b) {
@@ -774,11 +781,11 @@ __device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uin
         raise_error(p, sc, FDMOE_ERR_ROW_OVERFLOW, (uint32_t)myi);
       } else {
         const size_t rowg = (size_t)le * p.cap_rows + pos;
-        sc.fix_row[half][lane] = (int32_t)rowg;
-        sc.fix_owner[half][lane] = owner;
+        const size_t ent = (size_t)myi * p.send_stride + atomicAdd(&p.send_cnt[myi], 1u);
+        p.send_src[ent] = (int32_t)((tok << 4) | (uint32_t)lane);
+        p.send_dst[ent] = (int32_t)rowg;
         p.topk_idx[(size_t)tok * K + lane] = myi;
         p.topk_w[(size_t)tok * K + lane] = w;
-        p.dest_row[(size_t)tok * K + lane] = (int32_t)rowg;
         *reinterpret_cast<uint4*>(&p.peers[owner].meta[rowg]) =
             make_uint4(tok, (uint32_t)((p.rank << 8) | lane), __float_as_uint(w), 0u);
       }
@@ -786,85 +793,47 @@ __device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uin
   }
   epi_bar();
   prof_mark(p, sc, etid, 32);
-  if (live && !sc.abort) {
-    // the four warps of a half copy the staged row to its K destinations
-    for (int k = (ewarp & 3); k < K; k += 4) {
-      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.peers[sc.fix_owner[half][k]].packed) +
-                                            (size_t)sc.fix_row[half][k] * H);
-      for (int v = lane; v < H / 8; v += 32) dst[v] = sc.xrow[half][v];
-    }
-  }
-  ptx::fence_proxy_async();  // packed rows are read by TMA
-  epi_bar();
-  prof_mark(p, sc, etid, 33);
-  const uint32_t ntok = (tok_b != 0xffffffffu) ? 2u : 1u;
-  if (p.eager && !sc.abort && (uint32_t)etid < ntok * (uint32_t)K) {
-    const int hf = etid / K, k = etid % K;
-    const int rowg = sc.fix_row[hf][k], owner = sc.fix_owner[hf][k];
-    const uint32_t le = (uint32_t)rowg / (uint32_t)p.cap_rows, pos = (uint32_t)rowg % (uint32_t)p.cap_rows;
-    const uint32_t j = pos / 128u, nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
-    fence_acqrel<S>();
-    const uint32_t prev = atom_add<S>(&p.peers[owner].tile_landed[(size_t)le * p.MT + j], 1u);
-    if (prev + 1u == 128u) {
-      fence_acqrel<S>();
-      queue_push<S>(p, p.peers[owner], nt1, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
-        a = task_word(FDMOE_TASK_FFN1, le, i);
-        b = j;
-        c = 128u;
-      });
-    }
-  }
-  if (p.eager) epi_bar();
-  if (etid == 0) {
-    fence_acqrel<S>();
-    const uint32_t done = atomicAdd(&p.peers[p.rank].ctl->pack_done, ntok) + ntok;
-    if (done == (uint32_t)p.T) gate_phase_finished<S>(p);
-  }
+  if (etid == 0) count_gated<S>(p, (tok_b != 0xffffffffu) ? 2u : 1u);
   return true;
 }
 
-// ============================================================ FLUSH and FFN
-// FLUSH: every rank's gate phase is complete, so the per-expert row counts are
-// final.  Publishes FFN1 tasks for all tiles (or, in eager mode, only for the
-// partial last tile of each expert), ordered by expert so that tiles sharing
-// weights run close together.  Executed by the 256 epilogue threads.
+// ============================================================ GATED and FFN
+// GATED: every rank has finished gating, so the row counts of this rank's
+// experts and this rank's send lists are final.  Records the number of m-tiles
+// this rank will process (termination), then publishes this rank's PACK tasks:
+// 64-row pieces of its send lists, expert by expert, starting with the experts
+// of the next rank so that the ranks do not all send to the same owner at once.
 template <bool S>
-__device__ __noinline__ void flush_task(const FdmoeParams& p, SmemCtl& sc, int etid) {
+__device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int etid) {
   const FdmoePeer& me = p.peers[p.rank];
-  const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
   const int lane = etid & 31, w = etid >> 5;
-  // (the FLUSH task was taken from the queue with an acquire load that is ordered after every
-  // rank's row reservations, so the counts below are final)
-  // per-expert task and tile counts, then an exclusive prefix over the experts
-  // (shuffle scan inside each of the four warps that hold experts, warp totals
-  // through shared memory)
-  uint32_t full = 0, rem = 0, ntask = 0, ntile = 0;
-  if (etid < p.El) {
-    const uint32_t cnt = ld_relaxed<S>(&me.expert_cnt[etid]);
-    full = cnt / 128u;
-    rem = cnt % 128u;
-    ntile = full + (rem ? 1u : 0u);
-    ntask = p.eager ? (rem ? nt1 : 0u) : ntile * nt1;
+  // (the task was taken from the queue with an acquire load ordered after every rank's reservations)
+  uint32_t ntile = 0, npack = 0, ecnt = 0;
+  const int e_send = (etid < p.E) ? (int)(((uint32_t)((p.rank + 1) % p.world) * (uint32_t)p.El + (uint32_t)etid) % (uint32_t)p.E) : 0;
+  if (etid < p.El) ntile = (ld_relaxed<S>(&me.expert_cnt[etid]) + 127u) / 128u;
+  if (etid < p.E) {
+    ecnt = __ldcg(&p.send_cnt[e_send]);
+    npack = (ecnt + FDMOE_PACK_ROWS - 1) / FDMOE_PACK_ROWS;
   }
-  uint32_t inc_task = ntask, inc_tile = ntile;
+  uint32_t inc_pack = npack, inc_tile = ntile;
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
-    const uint32_t a = __shfl_up_sync(0xffffffffu, inc_task, off);
+    const uint32_t a = __shfl_up_sync(0xffffffffu, inc_pack, off);
     const uint32_t b = __shfl_up_sync(0xffffffffu, inc_tile, off);
     if (lane >= off) {
-      inc_task += a;
+      inc_pack += a;
       inc_tile += b;
     }
   }
   if (lane == 31 && w < 4) {
-    sc.pre[w] = inc_task;
+    sc.pre[w] = inc_pack;
     sc.pre[8 + w] = inc_tile;
   }
   epi_bar();
-  uint32_t off_task = 0, total = 0, mt = 0;
+  uint32_t off_pack = 0, total = 0, mt = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    if (i < w) off_task += sc.pre[i];
+    if (i < w) off_pack += sc.pre[i];
     total += sc.pre[i];
     mt += sc.pre[8 + i];
   }
@@ -874,23 +843,17 @@ __device__ __noinline__ void flush_task(const FdmoeParams& p, SmemCtl& sc, int e
   }
   epi_bar();
   const uint32_t t0 = sc.q_t0;
-  const uint32_t first = off_task + inc_task - ntask;  // exclusive prefix of this expert
-  for (uint32_t r = 0; r < ntask; ++r) {
-    uint32_t j, n, rows;
-    if (p.eager) {
-      j = full; n = r; rows = rem;
-    } else {
-      j = r / nt1; n = r - j * nt1; rows = (j < full) ? 128u : rem;
-    }
-    FdmoeSlot* s = &me.slots[(t0 + first + r) & (uint32_t)p.queue_mask];
-    s->a = task_word(FDMOE_TASK_FFN1, (uint32_t)etid, n);
-    s->b = j;
-    s->c = rows;
+  const uint32_t firstslot = off_pack + inc_pack - npack;  // exclusive prefix in sending order
+  for (uint32_t r = 0; r < npack; ++r) {
+    FdmoeSlot* sl = &me.slots[(t0 + firstslot + r) & (uint32_t)p.queue_mask];
+    sl->a = task_word(FDMOE_TASK_PACK, (uint32_t)e_send, 0u);
+    sl->b = r * FDMOE_PACK_ROWS;
+    sl->c = min((uint32_t)FDMOE_PACK_ROWS, ecnt - r * FDMOE_PACK_ROWS);
   }
   // one fence orders every payload above before every sequence word below
   fence_acqrel<false>();
-  for (uint32_t r = 0; r < ntask; ++r)
-    st_relaxed<false>(&me.slots[(t0 + first + r) & (uint32_t)p.queue_mask].seq, t0 + first + r + 1u);
+  for (uint32_t r = 0; r < npack; ++r)
+    st_relaxed<false>(&me.slots[(t0 + firstslot + r) & (uint32_t)p.queue_mask].seq, t0 + firstslot + r + 1u);
   epi_bar();
   if (etid == 0) {
     st_release<false>(&me.ctl->flush_done, 1u);
@@ -1081,9 +1044,9 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
   // so that all tiles are available at once.  Nothing to gate: the rank's "gate phase" is
   // finished at once (it may still serve its peers).
   if (p.mode != 2 && !sc.abort && tid == 0) {
-    const uint32_t n_tiles = (uint32_t)((p.T + p.gate_rows - 1) / p.gate_rows);
+    const uint32_t n_tiles = (p.T > 0 && p.gate_rows > 0) ? (uint32_t)((p.T + p.gate_rows - 1) / p.gate_rows) : 0u;
     if (n_tiles == 0) {
-      if (blockIdx.x == 0) gate_phase_finished<S>(p);
+      if (blockIdx.x == 0) gating_finished<S>(p);
     } else if (blockIdx.x < n_tiles) {
       const uint32_t mine = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
       queue_push<false>(p, me, mine, [](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
@@ -1303,7 +1266,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         ptx::tcgen05_fence_after();
         gate_epilogue<S>(p, sc, tmem_base + acc * kAccCols, &sc.tmem_empty[acc], q, h, lane, etid, ewarp, j);
       } else if (kind == FDMOE_TASK_PACK) {
-        pack_task<S>(p, sc, etid, ewarp, lane, j, rows);
+        pack_task<S>(p, sc, etid, ewarp, lane, e, j, rows);
       } else if (kind == FDMOE_TASK_GATEFIX) {
         if (!gatefix_task<S>(p, sc, stage, stage_it, etid, ewarp, lane, j, rows)) break;
         if (etid == 0) {
@@ -1388,8 +1351,8 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           atomicAdd(&ctl->tokens_combined, (uint32_t)(t_end - t_begin));
           maybe_close(p);
         }
-      } else if (kind == FDMOE_TASK_FLUSH) {
-        flush_task<S>(p, sc, etid);
+      } else if (kind == FDMOE_TASK_GATED) {
+        gated_task<S>(p, sc, etid);
       } else if (kind == FDMOE_TASK_TESTA || kind == FDMOE_TASK_TESTB) {
         // task-system self test: two dependent stages over a 256-element chunk
         int* ptr = p.test_buf + (size_t)j * kEpiThreads + etid;

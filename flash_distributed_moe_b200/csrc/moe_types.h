@@ -17,7 +17,7 @@ enum {
   FDMOE_TILE_N2 = 256,   // FFN2: hidden columns per tile
   FDMOE_TILE_K = 64,     // one 128-byte swizzle atom of bf16 per stage
   FDMOE_GATE_TOKENS = 128,  // tokens per gate tile (one tcgen05 M tile)
-  FDMOE_PACK_TOKENS = 8,    // tokens per PACK task (one per epilogue warp)
+  FDMOE_PACK_ROWS = 64,     // rows per PACK task (rows of one expert, sent by one rank)
 };
 
 // Task kinds held by the global work queue.
@@ -26,13 +26,13 @@ enum {
   FDMOE_TASK_FFN1 = 1,     // (expert, m_tile, n_tile, rows): SwiGLU tile
   FDMOE_TASK_FFN2 = 2,     // (expert, m_tile, n_tile, rows): down-projection tile
   FDMOE_TASK_COMBINE = 3,  // (token group): ordered sum over the K slots
-  FDMOE_TASK_FLUSH = 4,    // all ranks finished their gate phase: publish remaining tiles
+  FDMOE_TASK_GATED = 4,    // every rank has finished gating: row counts are final, start the dispatch
   FDMOE_TASK_TESTA = 5,    // task-system self test: x[i] *= 2 over a chunk, then push TESTB
   FDMOE_TASK_TESTB = 6,    // task-system self test: x[i] += 1 over a chunk
   FDMOE_TASK_EXIT = 7,
   FDMOE_TASK_GATE = 8,     // (token tile): gate GEMM, top-k, softmax, row reservation
-  FDMOE_TASK_PACK = 9,     // (first token, count): copy token rows into the owners' expert buffers
-  FDMOE_TASK_GATEFIX = 10, // (token, token): exact fp32 gate of nearly tied tokens, then their pack
+  FDMOE_TASK_PACK = 9,     // (expert, first entry, count): copy this rank's rows for one expert to its owner
+  FDMOE_TASK_GATEFIX = 10, // (token, token): exact fp32 gate of nearly tied tokens
 };
 
 // Status codes written by the kernel (first error wins).
@@ -82,9 +82,9 @@ typedef struct {
   uint32_t ready[32];  // ready[r] = launch epoch of peer r (written by peer r)
   // --- per-launch counters: [launch_begin, launch_end) is zeroed before each launch
   uint32_t launch_begin;
-  uint32_t pack_done;        // tokens of this rank whose rows are packed
+  uint32_t gated_tokens;     // tokens of this rank whose routing is decided
   uint32_t reserved0;
-  uint32_t ranks_done;       // ranks whose gate phase is finished (incl. this one)
+  uint32_t ranks_gated;      // ranks whose gating is finished (incl. this one)
   uint32_t flush_done;
   uint32_t mtiles_total;     // m-tiles of this rank's experts this launch
   uint32_t mtiles_done;      // m-tiles whose FFN2 is complete
@@ -100,7 +100,7 @@ typedef struct {
   FdmoeCtl* ctl;
   FdmoeSlot* slots;
   uint32_t* expert_cnt;    // [El]       rows allocated per local expert
-  uint32_t* tile_landed;   // [El * MT]  rows landed per (expert, m_tile)
+  uint32_t* landed;        // [El]       rows landed per local expert
   uint32_t* tok_arrivals;  // [groups]   rows returned per token group
   void* packed;            // bf16 [El * cap_rows, H]
   FdmoeRowMeta* meta;      // [El * cap_rows]
@@ -132,7 +132,6 @@ typedef struct {
   int32_t queue_mask;   // capacity - 1 (capacity is a power of two)
   int32_t combine_group;  // tokens per COMBINE task
   int32_t gate_rows;    // tokens per GATE task: 32, 64 or 128 (rows of the 128-row MMA tile that are used)
-  int32_t eager;        // publish full tiles as they land instead of at flush
   int32_t mode;         // 0 full layer; 2 static tasks only (no gate)
   int32_t debug_flags;  // timing experiments only (results become invalid): 1 skip FFN stores,
                         // 2 skip completion fences, 4 skip proxy fences, 8 skip the operand loads of FFN tiles
@@ -146,8 +145,11 @@ typedef struct {
   void* act;            // bf16 [El * cap_rows, I]
   int32_t* topk_idx;    // [max_tokens, K]
   float* topk_w;        // [max_tokens, K]
-  int32_t* dest_row;    // [max_tokens, K] row of (token, slot) in its owner's expert buffers
-  uint8_t* tok_flag;    // [max_tokens] 1 = token is handled by a GATEFIX task, not by PACK
+  // this rank's send lists, one per (global) expert: entry i of expert e is at [e * send_stride + i]
+  uint32_t* send_cnt;   // [E] entries per expert (zeroed per launch)
+  int32_t* send_src;    // token << 4 | slot
+  int32_t* send_dst;    // row in the owner's expert buffers
+  int32_t send_stride;  // = max tokens of this rank (an expert gets at most one row per token)
   uint32_t* ffn1_done;  // [El * MT]
   uint32_t* ffn2_done;  // [El * MT]
   uint32_t* status_host;  // mapped pinned word: first error code, readable without a sync

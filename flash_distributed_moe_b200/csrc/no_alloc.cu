@@ -134,7 +134,8 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
     const uint64_t rows_max = std::min<uint64_t>((uint64_t)g.max_tokens_sum * g.K, (uint64_t)g.El * g.cap_rows);
     const uint64_t mtiles = rows_max / FDMOE_TILE_M + g.El;
     const uint64_t tasks = mtiles * (g.I / FDMOE_TILE_N1 + g.H / FDMOE_TILE_N2) + g.groups + 64 +
-                           (uint64_t)g.max_tokens_max / 32 + (uint64_t)g.max_tokens_max / FDMOE_PACK_TOKENS +
+                           (uint64_t)g.max_tokens_max / 32 +
+                           (uint64_t)g.max_tokens_max * g.K / FDMOE_PACK_ROWS + g.E +
                            (uint64_t)g.max_tokens_max / 2 + 512;
     g.queue_cap = NextPow2(tasks + 4ull * d->grid + 256);
   }
@@ -147,10 +148,10 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   off += AlignUp((size_t)g.max_tokens_max * g.K * 4, 256);
   const size_t off_w = off;
   off += AlignUp((size_t)g.max_tokens_max * g.K * 4, 256);
-  const size_t off_dest = off;
-  off += AlignUp((size_t)g.max_tokens_max * g.K * 4, 256);
-  const size_t off_flag = off;
-  off += AlignUp((size_t)g.max_tokens_max, 256);
+  const size_t off_src = off;
+  off += AlignUp((size_t)g.E * g.max_tokens_max * 4, 256);
+  const size_t off_dst = off;
+  off += AlignUp((size_t)g.E * g.max_tokens_max * 4, 256);
   if (off > kScratchBytes) {
     MOE_ERROR_LOG("FlashMoeLaunchNoAlloc: this call needs %zu bytes of scratch, the fixed array holds %zu "
                   "(H=%d I=%d E=%d K=%d tokens=%d); use CreateLauncher/Launch for larger problems",
@@ -179,7 +180,7 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   me.ctl = reinterpret_cast<FdmoeCtl*>(base + L.ctl);
   me.slots = reinterpret_cast<FdmoeSlot*>(base + L.slots);
   me.expert_cnt = reinterpret_cast<uint32_t*>(base + L.expert_cnt);
-  me.tile_landed = reinterpret_cast<uint32_t*>(base + L.tile_landed);
+  me.landed = reinterpret_cast<uint32_t*>(base + L.landed);
   me.tok_arrivals = reinterpret_cast<uint32_t*>(base + L.tok_arrivals);
   me.packed = base + L.packed;
   me.meta = reinterpret_cast<FdmoeRowMeta*>(base + L.meta);
@@ -196,7 +197,6 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   p.MT = g.MT;
   p.queue_mask = (int32_t)(g.queue_cap - 1);
   p.combine_group = g.combine_group;
-  p.eager = 0;
   p.mode = 0;
   p.epoch = 1;
   p.timeout_ns = 2000ull * 1000000ull;
@@ -206,8 +206,10 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   p.act = base + off_act;
   p.topk_idx = reinterpret_cast<int32_t*>(base + off_idx);
   p.topk_w = reinterpret_cast<float*>(base + off_w);
-  p.dest_row = reinterpret_cast<int32_t*>(base + off_dest);
-  p.tok_flag = base + off_flag;
+  p.send_cnt = reinterpret_cast<uint32_t*>(base + L.send_cnt);
+  p.send_src = reinterpret_cast<int32_t*>(base + off_src);
+  p.send_dst = reinterpret_cast<int32_t*>(base + off_dst);
+  p.send_stride = g.max_tokens_max;
   p.ffn1_done = reinterpret_cast<uint32_t*>(base + L.ffn1_done);
   p.ffn2_done = reinterpret_cast<uint32_t*>(base + L.ffn2_done);
   NA_CHECK(fdmoe_kernel_launch(&p, d->grid, stream));
