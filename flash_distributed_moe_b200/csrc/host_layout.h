@@ -8,6 +8,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <algorithm>
+
 #include "moe_types.h"
 
 #ifndef MOE_ERROR_LOG
@@ -33,7 +35,7 @@ inline uint32_t NextPow2(uint64_t v) {
 // ranks, so a peer's regions are found from its base pointer alone.
 struct ArenaLayout {
   size_t ctl = 0;
-  size_t expert_cnt = 0, landed = 0, send_cnt = 0, tok_arrivals = 0, ffn1_done = 0, ffn2_done = 0;
+  size_t expert_cnt = 0, landed = 0, send_cnt = 0, ffn1_done = 0, ffn2_done = 0;
   size_t zero_begin = 0, zero_end = 0;  // per-launch reset range
   size_t slots = 0, meta = 0, ystage = 0, packed = 0;
   size_t total = 0;
@@ -44,9 +46,24 @@ struct Geometry {
   int max_tokens_local = 0;  // this rank
   int max_tokens_max = 0;    // largest over ranks (sizes token-indexed regions)
   int64_t max_tokens_sum = 0;  // all ranks (sizes expert buffers)
-  int cap_rows = 0, MT = 0, combine_group = 16, groups = 0;
+  int cap_rows = 0, MT = 0, combine_group = 16;  // combine_group: most tokens per COMBINE task
   uint32_t queue_cap = 0;
 };
+
+// Slots of a rank's task queue: at least every task one launch can publish there, so that a
+// slot is never reused within a launch.  Tile tasks of the rank's experts, COMBINE tasks (at
+// most max_tokens / combine_group + one wave of `grid`), GATED, this rank's GATE tasks (>= 32
+// tokens each), PACK pieces (FDMOE_PACK_ROWS rows, one ragged piece per expert) and GATEFIX
+// tasks (two tokens each, every token in the worst case), plus EXIT tickets of every worker.
+inline uint32_t QueueCapacity(const Geometry& g, int grid) {
+  const uint64_t rows_max = std::min<uint64_t>((uint64_t)g.max_tokens_sum * g.K, (uint64_t)g.El * g.cap_rows);
+  const uint64_t mtiles = rows_max / FDMOE_TILE_M + g.El;
+  const uint64_t tasks = mtiles * (g.I / FDMOE_TILE_N1 + g.H / FDMOE_TILE_N2) +
+                         (uint64_t)g.max_tokens_max / std::max(1, g.combine_group) + grid + 64 +
+                         (uint64_t)g.max_tokens_max / 32 + (uint64_t)g.max_tokens_max * g.K / FDMOE_PACK_ROWS + g.E +
+                         (uint64_t)g.max_tokens_max / 2 + 1024;
+  return NextPow2(tasks + 4ull * grid + 1024);
+}
 
 inline ArenaLayout MakeLayout(const Geometry& g) {
   ArenaLayout L;
@@ -60,8 +77,6 @@ inline ArenaLayout MakeLayout(const Geometry& g) {
   off += AlignUp((size_t)g.El * 4, 128);
   L.send_cnt = off;
   off += AlignUp((size_t)g.E * 4, 128);
-  L.tok_arrivals = off;
-  off += AlignUp((size_t)g.groups * 4, 128);
   L.ffn1_done = off;
   off += AlignUp((size_t)g.El * g.MT * 4, 128);
   L.ffn2_done = off;

@@ -211,18 +211,7 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   g_.cap_rows = (int)AlignUp((size_t)std::max<int64_t>(g_.max_tokens_sum, 1), FDMOE_TILE_M);
   g_.MT = g_.cap_rows / FDMOE_TILE_M;
   g_.combine_group = std::max(1, EnvInt("FLASHMOE_COMBINE_GROUP", 16));
-  g_.groups = (g_.max_tokens_max + g_.combine_group - 1) / g_.combine_group + 1;
-  {
-    const uint64_t rows_max = std::min<uint64_t>((uint64_t)g_.max_tokens_sum * g_.K, (uint64_t)g_.El * g_.cap_rows);
-    const uint64_t mtiles = rows_max / FDMOE_TILE_M + g_.El;
-    // tile tasks + COMBINE groups + GATED + this rank's GATE (>= 32 tokens each), PACK (64 rows each)
-    // and GATEFIX tasks (2 tokens each, every token in the worst case)
-    const uint64_t tasks = mtiles * (g_.I / FDMOE_TILE_N1 + g_.H / FDMOE_TILE_N2) + g_.groups + 64 +
-                           (uint64_t)g_.max_tokens_max / 32 +
-                           (uint64_t)g_.max_tokens_max * g_.K / FDMOE_PACK_ROWS + g_.E +
-                           (uint64_t)g_.max_tokens_max / 2 + 1024;
-    g_.queue_cap = NextPow2(tasks + 4ull * grid_ + 1024);
-  }
+  g_.queue_cap = QueueCapacity(g_, grid_);
   layout_ = MakeLayout(g_);
 
   // ---- allocations
@@ -232,7 +221,8 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&topk_idx_), std::max<size_t>(4, (size_t)maxTokens * g_.K * 4)));
   CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&topk_w_), std::max<size_t>(4, (size_t)maxTokens * g_.K * 4)));
   {
-    const size_t list_bytes = std::max<size_t>(16, (size_t)g_.E * maxTokens * 4);
+    // stride rounded to 4 entries and 16 bytes of slack: PACK reads the lists with 16-byte loads
+    const size_t list_bytes = (size_t)g_.E * AlignUp((size_t)std::max(maxTokens, 1), 4) * 4 + 16;
     CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&send_src_), list_bytes));
     CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&send_dst_), list_bytes));
   }
@@ -304,7 +294,6 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
     pv.slots = reinterpret_cast<FdmoeSlot*>(b + layout_.slots);
     pv.expert_cnt = reinterpret_cast<uint32_t*>(b + layout_.expert_cnt);
     pv.landed = reinterpret_cast<uint32_t*>(b + layout_.landed);
-    pv.tok_arrivals = reinterpret_cast<uint32_t*>(b + layout_.tok_arrivals);
     pv.packed = b + layout_.packed;
     pv.meta = reinterpret_cast<FdmoeRowMeta*>(b + layout_.meta);
     pv.ystage = b + layout_.ystage;
@@ -329,7 +318,7 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   params_.topk_w = topk_w_;
   params_.send_src = send_src_;
   params_.send_dst = send_dst_;
-  params_.send_stride = std::max(maxTokens, 1);
+  params_.send_stride = (int32_t)AlignUp((size_t)std::max(maxTokens, 1), 4);
   params_.send_cnt = reinterpret_cast<uint32_t*>(arena_ + layout_.send_cnt);
   params_.ffn1_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn1_done);
   params_.ffn2_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn2_done);

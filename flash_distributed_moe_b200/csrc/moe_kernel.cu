@@ -303,6 +303,16 @@ __device__ __forceinline__ void queue_push(const FdmoeParams& p, const FdmoePeer
   for (uint32_t i = 0; i < n; ++i) st_relaxed<S>(&q.slots[(t0 + i) & (uint32_t)p.queue_mask].seq, t0 + i + 1u);
 }
 
+// Tokens per COMBINE task of a rank with T tokens: at most `cap`, and such that the tasks fill
+// whole waves of `grid` workers (e.g. 4096 tokens on 148 workers: 14 tokens, 293 tasks, two
+// waves).  A pure function of T, so that a peer can publish another rank's COMBINE tasks.
+__device__ __forceinline__ uint32_t combine_group_of(int T, int grid, int cap) {
+  if (T <= 0) return 1u;
+  const int waves = (T + cap * grid - 1) / (cap * grid);
+  const int g = (T + waves * grid - 1) / (waves * grid);
+  return (uint32_t)max(1, min(g, cap));
+}
+
 __device__ __forceinline__ uint32_t task_word(uint32_t kind, uint32_t e, uint32_t n) {
   return kind | (e << 8) | (n << 20);
 }
@@ -629,48 +639,74 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
 
 // ===================================================================== PACK
 // Sends `count` rows of one expert (entries [first, first + count) of this rank's
-// send list for it) to the expert's owner: one warp per row, 16-byte stores into
-// the owner's expert buffer (local or over NVLink).  The sender whose rows
-// complete the expert (all ranks have finished gating before any PACK task
+// send list for it) to the expert's owner.  The rows travel as bulk copies:
+// the TMA warp brings up to pack_rows_per_stage() token rows into a pipeline
+// stage, the lanes of the first epilogue warp send one row each from there into
+// the owner's expert buffer (local, or a peer's over NVLink).  The sender whose
+// rows complete the expert (all ranks have finished gating before any PACK task
 // exists, so the expert's row count is final) publishes all its FFN1 tile tasks
 // on the owner's queue, m-tile major, so that the tiles of one expert run
 // together and share its weights through L2.
+__device__ __forceinline__ uint32_t pack_rows_per_stage(int H) {
+  return min(16u, (uint32_t)kStageBytes / ((uint32_t)H * 2u));
+}
+
+// TMA-warp side of a PACK task (one thread): brings the token rows of the piece into the
+// pipeline stages, up to pack_rows_per_stage() rows per stage.  The source indices of the
+// next stage are fetched while the current one is waited for and issued.
+__device__ __noinline__ bool pack_loads(const FdmoeParams& p, SmemCtl& sc, uint8_t* stage, uint32_t& stage_it,
+                                        uint32_t e, uint32_t first, uint32_t count) {
+  const uint32_t rowb = (uint32_t)p.H * 2u, rps = pack_rows_per_stage(p.H);
+  const int32_t* src_list = p.send_src + (size_t)e * p.send_stride + first;
+  const uint8_t* xb = reinterpret_cast<const uint8_t*>(p.x);
+  int32_t cur[16], nxt[16];
+#pragma unroll
+  for (uint32_t i = 0; i < 16; ++i) cur[i] = (i < rps && i < count) ? __ldcg(src_list + i) : 0;
+  for (uint32_t b0 = 0; b0 < count; b0 += rps, ++stage_it) {
+    const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
+    const uint32_t nrows = min(rps, count - b0);
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) nxt[i] = (i < rps && b0 + rps + i < count) ? __ldcg(src_list + b0 + rps + i) : 0;
+    if (!wait_bar(p, sc, &sc.empty_bar[s], sph ^ 1u, FDMOE_ERR_TIMEOUT_STAGE)) return false;
+    ptx::mbar_expect_tx(&sc.full_bar[s], nrows * rowb);
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i)
+      if (i < nrows)
+        ptx::bulk_load_1d(stage + s * kStageBytes + i * rowb, xb + (size_t)(cur[i] >> 4) * rowb, rowb, &sc.full_bar[s]);
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) cur[i] = nxt[i];
+  }
+  return true;
+}
+
 template <bool S>
-__device__ __noinline__ void pack_task(const FdmoeParams& p, SmemCtl& sc, int etid, int ewarp, int lane, uint32_t e,
-                                       uint32_t first, uint32_t count) {
+__device__ __noinline__ bool pack_task(const FdmoeParams& p, SmemCtl& sc, uint8_t* stage, uint32_t& stage_it, int etid,
+                                       int ewarp, int lane, uint32_t e, uint32_t first, uint32_t count) {
   const int H = p.H;
-  const bf16* x = reinterpret_cast<const bf16*>(p.x);
+  const uint32_t rowb = (uint32_t)H * 2u, rps = pack_rows_per_stage(H);
   const int owner = (int)e / p.El, le = (int)e - owner * p.El;
   const FdmoePeer& op = p.peers[owner];
-  bf16* packed = reinterpret_cast<bf16*>(op.packed);
-  const int32_t* src_list = p.send_src + (size_t)e * p.send_stride + first;
+  uint8_t* packed = reinterpret_cast<uint8_t*>(op.packed);
   const int32_t* dst_list = p.send_dst + (size_t)e * p.send_stride + first;
-  // a warp takes rows ewarp, ewarp + 8, ... two at a time, so that the loads of both are in flight
-  for (uint32_t r0 = ewarp; r0 < count; r0 += 16) {
-    const bool has1 = r0 + 8 < count;
-    const int s0 = __ldcg(src_list + r0), d0 = __ldcg(dst_list + r0);
-    const int s1 = has1 ? __ldcg(src_list + r0 + 8) : s0, d1 = has1 ? __ldcg(dst_list + r0 + 8) : d0;
-    const uint4* src0 = reinterpret_cast<const uint4*>(x + (size_t)(s0 >> 4) * H);
-    const uint4* src1 = reinterpret_cast<const uint4*>(x + (size_t)(s1 >> 4) * H);
-    uint4* dst0 = reinterpret_cast<uint4*>(packed + (size_t)d0 * H);
-    uint4* dst1 = reinterpret_cast<uint4*>(packed + (size_t)d1 * H);
-    for (int vbase = 0; vbase < H / 8; vbase += 256) {
-      uint4 a[8], b[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int vi = vbase + lane + 32 * i;
-        a[i] = (vi < H / 8) ? src0[vi] : make_uint4(0, 0, 0, 0);
-        b[i] = (has1 && vi < H / 8) ? src1[vi] : make_uint4(0, 0, 0, 0);
+  for (uint32_t b0 = 0; b0 < count; b0 += rps, ++stage_it) {
+    const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
+    const uint32_t nrows = min(rps, count - b0);
+    int32_t d = 0;
+    if (ewarp == 0 && (uint32_t)lane < nrows) d = __ldcg(dst_list + b0 + lane);
+    if (!epi_vote_all(wait_bar(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE))) return false;
+    if (ewarp == 0) {
+      if ((uint32_t)lane < nrows) {
+        ptx::bulk_store_1d(packed + (size_t)d * rowb, stage + s * kStageBytes + (uint32_t)lane * rowb, rowb);
+        ptx::bulk_commit_group();
+        ptx::bulk_wait_group_read0();
       }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int vi = vbase + lane + 32 * i;
-        if (vi < H / 8) {
-          dst0[vi] = a[i];
-          if (has1) dst1[vi] = b[i];
-        }
-      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&sc.empty_bar[s]);
     }
+  }
+  if (ewarp == 0) {
+    ptx::bulk_wait_group0();  // this lane's rows are written
+    __syncwarp();
   }
   ptx::fence_proxy_async();  // packed rows are read by TMA
   epi_bar();
@@ -707,6 +743,7 @@ __device__ __noinline__ void pack_task(const FdmoeParams& p, SmemCtl& sc, int et
     }
   }
   epi_bar();  // sc.flag / sc.q_t0 may be rewritten by the next task only after everyone has read them
+  return true;
 }
 
 // ================================================================== GATEFIX
@@ -1074,8 +1111,8 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         ptx::mbar_arrive(&sc.ring_full[r]);
         const uint32_t kind = t.a & 0xffu;
         if (kind == FDMOE_TASK_EXIT) break;
-        if (kind != FDMOE_TASK_FFN1 && kind != FDMOE_TASK_FFN2 && kind != FDMOE_TASK_COMBINE) {
-          // Only tile tasks (and COMBINE, whose rows are prefetched by bulk copies) profit from being queued behind one another (their loads and
+        if (kind != FDMOE_TASK_FFN1 && kind != FDMOE_TASK_FFN2 && kind != FDMOE_TASK_COMBINE && kind != FDMOE_TASK_PACK) {
+          // Only tile tasks (and COMBINE / PACK, whose rows travel as bulk copies) profit from being queued behind one another (their loads and
           // MMAs run ahead of the epilogue).  Behind a long task of another kind a claimed
           // ticket would just sit here while other workers idle: wait until it is done.
           if (!wait_bar(p, sc, &sc.ring_empty[r], ph, FDMOE_ERR_TIMEOUT_RING)) break;
@@ -1149,8 +1186,11 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
                                (int32_t)((kb + i) * FDMOE_TILE_K), 0);
           }
           if (!ok) break;
+        } else if (kind == FDMOE_TASK_PACK) {
+          const bool ok = pack_loads(p, sc, stage, stage_it, (t.a >> 8) & 0xfffu, t.b, t.c);
+          if (!ok) break;
         } else if (kind == FDMOE_TASK_COMBINE) {
-          const int t_begin = (int)t.b * p.combine_group, t_end = min(t_begin + p.combine_group, p.T);
+          const int t_begin = (int)t.b, t_end = t_begin + (int)t.c;
           const bf16* ys = reinterpret_cast<const bf16*>(me.ystage);
           ptx::fence_proxy_async();  // the rows were written with generic stores
           bool ok = true;
@@ -1210,7 +1250,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           }
           if (!ok) break;
           ptx::umma_commit(&sc.tmem_full[acc]);
-        } else if (kind == FDMOE_TASK_GATEFIX || kind == FDMOE_TASK_COMBINE) {
+        } else if (kind == FDMOE_TASK_GATEFIX || kind == FDMOE_TASK_COMBINE || kind == FDMOE_TASK_PACK) {
           // The stages of these tasks are consumed by the epilogue warps.  This warp must not
           // run ahead of them: a stage barrier only tells phases apart by parity, so a waiter
           // more than one phase ahead would take an old completion for its own.  Wait until
@@ -1233,8 +1273,11 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           if (!ok) break;
           if (kind == FDMOE_TASK_GATEFIX) {
             stage_it += (nkb1 + kFixBlocks - 1) / kFixBlocks;
+          } else if (kind == FDMOE_TASK_PACK) {
+            const uint32_t rps = pack_rows_per_stage(p.H);
+            stage_it += (t.c + rps - 1u) / rps;
           } else {
-            const int t_begin = (int)t.b * p.combine_group, t_end = min(t_begin + p.combine_group, p.T);
+            const int t_begin = (int)t.b, t_end = t_begin + (int)t.c;
             stage_it += (uint32_t)((t_end - t_begin) * ((p.H + kCombineCols - 1) / kCombineCols));
           }
         }
@@ -1266,7 +1309,11 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         ptx::tcgen05_fence_after();
         gate_epilogue<S>(p, sc, tmem_base + acc * kAccCols, &sc.tmem_empty[acc], q, h, lane, etid, ewarp, j);
       } else if (kind == FDMOE_TASK_PACK) {
-        pack_task<S>(p, sc, etid, ewarp, lane, e, j, rows);
+        if (!pack_task<S>(p, sc, stage, stage_it, etid, ewarp, lane, e, j, rows)) break;
+        if (etid == 0) {
+          __threadfence_block();
+          sc.skip_done = sc.skip_done + 1u;
+        }
       } else if (kind == FDMOE_TASK_GATEFIX) {
         if (!gatefix_task<S>(p, sc, stage, stage_it, etid, ewarp, lane, j, rows)) break;
         if (etid == 0) {
@@ -1307,7 +1354,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         if (etid == 0) prof_event(p, sc, kind + 16u, pt1, pta, prof_now());
       } else if (kind == FDMOE_TASK_COMBINE) {
         // out[t, :] = sum over slots k = 0..K-1 (in that order, fp32) of y[t, k, :]
-        const int t_begin = (int)j * p.combine_group, t_end = min(t_begin + p.combine_group, p.T);
+        const int t_begin = (int)j, t_end = t_begin + (int)rows;
         bf16* outp = reinterpret_cast<bf16*>(p.out);
         bool ok = true;
         for (int tk = t_begin; tk < t_end && ok; ++tk) {
@@ -1435,24 +1482,55 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         }
         last = __shfl_sync(0xffffffffu, last, 0);
         if (last) {
-          // every hidden-column tile of this m-tile is stored: tell the home ranks
+          // every hidden-column tile of this m-tile is stored: tell each home rank how many
+          // of its rows that makes (one counter update per home rank and m-tile)
+          uint32_t cnt[FDMOE_MAX_WORLD];
+#pragma unroll
+          for (int w = 0; w < FDMOE_MAX_WORLD; ++w) cnt[w] = 0u;
           for (uint32_t r = lane; r < rows; r += 32) {
             const uint4 mraw = ld_cg_u4(&me.meta[(size_t)e * p.cap_rows + (size_t)j * 128 + r]);
-            const int token = (int)mraw.x, home = (int)mraw.y >> 8;
-            const uint32_t g = (uint32_t)(token / p.combine_group);
-            const FdmoePeer& hp = p.peers[home];
+            const int home = (int)mraw.y >> 8;
+#pragma unroll
+            for (int w = 0; w < FDMOE_MAX_WORLD; ++w) cnt[w] += (home == w) ? 1u : 0u;
+          }
+          uint32_t mine = 0u;
+#pragma unroll
+          for (int w = 0; w < FDMOE_MAX_WORLD; ++w) {
+            const uint32_t c = __reduce_add_sync(0xffffffffu, cnt[w]);
+            if (lane == w) mine = c;
+          }
+          uint32_t th = 0u;
+          if (lane < p.world && mine) {
+            const FdmoePeer& hp = p.peers[lane];
             fence_acqrel<S>();
-            const uint32_t prev = atom_add<S>(&hp.tok_arrivals[g], 1u);
-            const int th = (home == p.rank) ? p.T : (int)ld_relaxed<S>(&hp.ctl->tokens_launch);
-            const int gt = min(p.combine_group, th - (int)g * p.combine_group);
-            if (prev + 1u == (uint32_t)(gt * p.K)) {
+            const uint32_t prev = atom_add<S>(&hp.ctl->rows_arrived, mine);
+            const uint32_t tl = (lane == p.rank) ? (uint32_t)p.T : ld_relaxed<S>(&hp.ctl->tokens_launch);
+            if (prev + mine == tl * (uint32_t)p.K) th = tl;  // that home rank has all its rows
+          }
+          // ranks completed by this m-tile get their COMBINE tasks, published by the whole warp
+          uint32_t complete = __ballot_sync(0xffffffffu, th != 0u);
+          while (complete) {
+            const int home = __ffs(complete) - 1;
+            complete &= complete - 1u;
+            const uint32_t tl = __shfl_sync(0xffffffffu, th, home);
+            const FdmoePeer& hp = p.peers[home];
+            const uint32_t grp = combine_group_of((int)tl, (int)gridDim.x, p.combine_group);
+            const uint32_t ntask = (tl + grp - 1u) / grp;
+            uint32_t t0 = 0u;
+            if (lane == 0) {
               fence_acqrel<S>();
-              queue_push<S>(p, hp, 1u, [&](uint32_t, uint32_t& a, uint32_t& b, uint32_t& c) {
-                a = FDMOE_TASK_COMBINE;
-                b = g;
-                c = 0;
-              });
+              t0 = atom_add<S>(&hp.ctl->q_head, ntask);
             }
+            t0 = __shfl_sync(0xffffffffu, t0, 0);
+            for (uint32_t i = lane; i < ntask; i += 32) {
+              FdmoeSlot* sl = &hp.slots[(t0 + i) & (uint32_t)p.queue_mask];
+              sl->a = FDMOE_TASK_COMBINE;
+              sl->b = i * grp;
+              sl->c = min(grp, tl - i * grp);
+            }
+            fence_acqrel<S>();  // each lane: its payloads (and the arrival counts seen above) before its sequence words
+            for (uint32_t i = lane; i < ntask; i += 32)
+              st_relaxed<S>(&hp.slots[(t0 + i) & (uint32_t)p.queue_mask].seq, t0 + i + 1u);
           }
           __syncwarp();
           if (lane == 0) {

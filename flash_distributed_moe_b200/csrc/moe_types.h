@@ -17,7 +17,7 @@ enum {
   FDMOE_TILE_N2 = 256,   // FFN2: hidden columns per tile
   FDMOE_TILE_K = 64,     // one 128-byte swizzle atom of bf16 per stage
   FDMOE_GATE_TOKENS = 128,  // tokens per gate tile (one tcgen05 M tile)
-  FDMOE_PACK_ROWS = 64,     // rows per PACK task (rows of one expert, sent by one rank)
+  FDMOE_PACK_ROWS = 72,     // rows per PACK task (rows of one expert, sent by one rank)
 };
 
 // Task kinds held by the global work queue.
@@ -83,7 +83,7 @@ typedef struct {
   // --- per-launch counters: [launch_begin, launch_end) is zeroed before each launch
   uint32_t launch_begin;
   uint32_t gated_tokens;     // tokens of this rank whose routing is decided
-  uint32_t reserved0;
+  uint32_t rows_arrived;     // weighted rows of this rank's tokens that have come back (T*K when complete)
   uint32_t ranks_gated;      // ranks whose gating is finished (incl. this one)
   uint32_t flush_done;
   uint32_t mtiles_total;     // m-tiles of this rank's experts this launch
@@ -101,7 +101,6 @@ typedef struct {
   FdmoeSlot* slots;
   uint32_t* expert_cnt;    // [El]       rows allocated per local expert
   uint32_t* landed;        // [El]       rows landed per local expert
-  uint32_t* tok_arrivals;  // [groups]   rows returned per token group
   void* packed;            // bf16 [El * cap_rows, H]
   FdmoeRowMeta* meta;      // [El * cap_rows]
   void* ystage;            // bf16 [max_tokens, K, H]
@@ -130,7 +129,7 @@ typedef struct {
   int32_t cap_rows;     // rows per expert buffer (multiple of 128)
   int32_t MT;           // cap_rows / 128
   int32_t queue_mask;   // capacity - 1 (capacity is a power of two)
-  int32_t combine_group;  // tokens per COMBINE task
+  int32_t combine_group;  // most tokens per COMBINE task
   int32_t gate_rows;    // tokens per GATE task: 32, 64 or 128 (rows of the 128-row MMA tile that are used)
   int32_t mode;         // 0 full layer; 2 static tasks only (no gate)
   int32_t debug_flags;  // timing experiments only (results become invalid): 1 skip FFN stores,

@@ -129,16 +129,7 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   g.cap_rows = (int)AlignUp((size_t)g.max_tokens_sum, FDMOE_TILE_M);
   g.MT = g.cap_rows / FDMOE_TILE_M;
   g.combine_group = 16;
-  g.groups = (g.max_tokens_max + g.combine_group - 1) / g.combine_group + 1;
-  {
-    const uint64_t rows_max = std::min<uint64_t>((uint64_t)g.max_tokens_sum * g.K, (uint64_t)g.El * g.cap_rows);
-    const uint64_t mtiles = rows_max / FDMOE_TILE_M + g.El;
-    const uint64_t tasks = mtiles * (g.I / FDMOE_TILE_N1 + g.H / FDMOE_TILE_N2) + g.groups + 64 +
-                           (uint64_t)g.max_tokens_max / 32 +
-                           (uint64_t)g.max_tokens_max * g.K / FDMOE_PACK_ROWS + g.E +
-                           (uint64_t)g.max_tokens_max / 2 + 512;
-    g.queue_cap = NextPow2(tasks + 4ull * d->grid + 256);
-  }
+  g.queue_cap = QueueCapacity(g, d->grid);
   const ArenaLayout L = MakeLayout(g);
   // regions the launcher allocates separately follow the arena inside the same array
   size_t off = AlignUp(L.total, 1024);
@@ -149,9 +140,9 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   const size_t off_w = off;
   off += AlignUp((size_t)g.max_tokens_max * g.K * 4, 256);
   const size_t off_src = off;
-  off += AlignUp((size_t)g.E * g.max_tokens_max * 4, 256);
+  off += AlignUp((size_t)g.E * AlignUp((size_t)g.max_tokens_max, 4) * 4 + 16, 256);
   const size_t off_dst = off;
-  off += AlignUp((size_t)g.E * g.max_tokens_max * 4, 256);
+  off += AlignUp((size_t)g.E * AlignUp((size_t)g.max_tokens_max, 4) * 4 + 16, 256);
   if (off > kScratchBytes) {
     MOE_ERROR_LOG("FlashMoeLaunchNoAlloc: this call needs %zu bytes of scratch, the fixed array holds %zu "
                   "(H=%d I=%d E=%d K=%d tokens=%d); use CreateLauncher/Launch for larger problems",
@@ -181,7 +172,6 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   me.slots = reinterpret_cast<FdmoeSlot*>(base + L.slots);
   me.expert_cnt = reinterpret_cast<uint32_t*>(base + L.expert_cnt);
   me.landed = reinterpret_cast<uint32_t*>(base + L.landed);
-  me.tok_arrivals = reinterpret_cast<uint32_t*>(base + L.tok_arrivals);
   me.packed = base + L.packed;
   me.meta = reinterpret_cast<FdmoeRowMeta*>(base + L.meta);
   me.ystage = base + L.ystage;
@@ -209,7 +199,7 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   p.send_cnt = reinterpret_cast<uint32_t*>(base + L.send_cnt);
   p.send_src = reinterpret_cast<int32_t*>(base + off_src);
   p.send_dst = reinterpret_cast<int32_t*>(base + off_dst);
-  p.send_stride = g.max_tokens_max;
+  p.send_stride = (int32_t)AlignUp((size_t)g.max_tokens_max, 4);
   p.ffn1_done = reinterpret_cast<uint32_t*>(base + L.ffn1_done);
   p.ffn2_done = reinterpret_cast<uint32_t*>(base + L.ffn2_done);
   NA_CHECK(fdmoe_kernel_launch(&p, d->grid, stream));

@@ -82,6 +82,13 @@ int FlashMoeTestTaskSystem(FlashMoeHandle h, int32_t* data, int n, void* stream)
 int FlashMoeTestQueueGemm(FlashMoeHandle h, const uint32_t* rowsPerExpertHost, const void* A,
                           void* out, void* stream);
 
+/* Self-test of the CTA-pair tensor-core primitive under the FFN tiles (no counterpart in the
+ * reference): one cluster of two CTAs computes D[256, N] = W[256, K] * X[N, K]^T with
+ * tcgen05.mma.cta_group::2, X arriving in boxes of `boxRows` rows.  W, X bf16 and D fp32 are
+ * device pointers; N a multiple of 16 in [16, 256], K a multiple of 64, boxRows a multiple of 8
+ * dividing N/2.  Synchronous. */
+int FlashMoeTestPairGemm(const void* W, const void* X, float* D, int N, int K, int boxRows, void* stream);
+
 /* The whole layer in one call that allocates nothing (no counterpart in the reference, whose
  * launcher always allocates its scratch in Init, src/hip/launcher/moeKernelLauncher.hip:139-165).
  * For callers that may not touch the device allocator: an engine that has frozen its memory pool,
