@@ -50,7 +50,7 @@ def lib() -> C.CDLL:
     L.FlashMoeDebugRead.argtypes = [vp, C.c_int, vp, C.c_size_t, C.c_size_t]
     L.FlashMoeTestTaskSystem.argtypes = [vp, vp, C.c_int, vp]
     L.FlashMoeTestQueueGemm.argtypes = [vp, C.POINTER(C.c_uint32), vp, vp, vp]
-    L.FlashMoeTestPairGemm.argtypes = [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp]
+    L.FlashMoeTestPairGemm.argtypes = [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_uint), vp]
     L.FlashMoeLaunchNoAlloc.argtypes = [vp, vp, vp, vp, vp, C.c_int, C.POINTER(FlashMoeConfig), vp]
     L.FlashMoeLaunchNoAlloc.restype = C.c_int
     L.FlashMoeErrorString.argtypes = [C.c_int]

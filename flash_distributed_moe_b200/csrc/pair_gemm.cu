@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/flashmoe_c.h"
 #include "host_layout.h"
@@ -15,7 +16,7 @@
 namespace fdmoe {
 namespace {
 
-constexpr int kPgStages = 4;
+constexpr int kPgStages = 6;
 constexpr int kPgStageA = 128 * 64 * 2;  // 16 KB: 128 W rows x 64 k
 constexpr int kPgStageB = 128 * 64 * 2;  // up to 128 X rows x 64 k
 constexpr int kPgStageBytes = kPgStageA + kPgStageB;
@@ -58,7 +59,7 @@ pair_gemm_kernel(const __grid_constant__ FdmoeTensorMap tm_w, const __grid_const
 
   if (tid == 0) {
     for (int s = 0; s < kPgStages; ++s) {
-      ptx::mbar_init(&c.full_bar[s], 2);  // one arrive.expect_tx per CTA
+      ptx::mbar_init(&c.full_bar[s], 1);  // the even CTA's arrival, which announces the bytes of both
       ptx::mbar_init(&c.empty_bar[s], 1);
     }
     ptx::mbar_init(&c.tmem_full, 1);
@@ -76,12 +77,12 @@ pair_gemm_kernel(const __grid_constant__ FdmoeTensorMap tm_w, const __grid_const
 
   if (warp == 0 && lane == 0) {
     // producer: this CTA's share of both operands, completion counted on the even CTA's barrier
-    const uint32_t bytes = (uint32_t)(128 + nhalf) * 64u * 2u;
+    const uint32_t pair_bytes = 2u * (uint32_t)(128 + nhalf) * 64u * 2u;
     for (uint32_t kb = 0; kb < nkb; ++kb) {
       const uint32_t s = kb % kPgStages, ph = (kb / kPgStages) & 1u;
       if (!pg_wait(c, &c.empty_bar[s], ph ^ 1u, status, 1u)) break;
       const uint32_t full0 = ptx::map_to_cta(ptx::smem_u32(&c.full_bar[s]), 0u);
-      ptx::mbar_expect_tx_cluster(full0, bytes);
+      if (cta == 0u) ptx::mbar_expect_tx(&c.full_bar[s], pair_bytes);
       uint8_t* sa = stage + s * kPgStageBytes;
       ptx::tma_load_2d_pair(sa, &tm_w, full0, (int32_t)(kb * 64u), (int32_t)(cta * 128u));
       for (int r = 0; r < nhalf; r += box_rows)
@@ -90,6 +91,7 @@ pair_gemm_kernel(const __grid_constant__ FdmoeTensorMap tm_w, const __grid_const
   } else if (warp == 1 && lane == 0 && cta == 0) {
     const uint32_t idesc = ptx::make_idesc_bf16(256, (uint32_t)N);
     bool ok = true;
+    const uint64_t t_begin = ptx::globaltimer_ns();
     for (uint32_t kb = 0; kb < nkb && ok; ++kb) {
       const uint32_t s = kb % kPgStages, ph = (kb / kPgStages) & 1u;
       ok = pg_wait(c, &c.full_bar[s], ph, status, 2u);
@@ -106,6 +108,7 @@ pair_gemm_kernel(const __grid_constant__ FdmoeTensorMap tm_w, const __grid_const
     if (ok) {
       ptx::umma_commit_pair(ptx::smem_u32(&c.tmem_full));
       ptx::umma_commit_pair(ptx::map_to_cta(ptx::smem_u32(&c.tmem_full), 1u));
+      if (blockIdx.x == 0) status[1] = (uint32_t)(ptx::globaltimer_ns() - t_begin);  // main loop, first wait to last issue
     }
   }
   __syncwarp();
@@ -136,7 +139,8 @@ pair_gemm_kernel(const __grid_constant__ FdmoeTensorMap tm_w, const __grid_const
 }  // namespace
 }  // namespace fdmoe
 
-extern "C" int FlashMoeTestPairGemm(const void* W, const void* X, float* D, int N, int K, int boxRows, void* stream_) {
+extern "C" int FlashMoeTestPairGemm(const void* W, const void* X, float* D, int N, int K, int boxRows,
+                                    unsigned* mainLoopNs, void* stream_) {
   using namespace fdmoe;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (!W || !X || !D || N < 16 || N > 256 || N % 16 != 0 || K < 64 || K % 64 != 0 || boxRows < 8 || boxRows % 8 != 0 ||
@@ -153,11 +157,14 @@ extern "C" int FlashMoeTestPairGemm(const void* W, const void* X, float* D, int 
   e = cudaFuncSetAttribute(pair_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return (int)e;
   uint32_t* status = nullptr;
-  e = cudaMalloc(reinterpret_cast<void**>(&status), 4);
+  e = cudaMalloc(reinterpret_cast<void**>(&status), 8);
   if (e != cudaSuccess) return (int)e;
-  cudaMemsetAsync(status, 0, 4, stream);
+  cudaMemsetAsync(status, 0, 8, stream);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2, 1, 1);
+  // (experiments) several clusters computing the same product, to load the memory system
+  const char* nc = getenv("FLASHMOE_PAIR_CLUSTERS");
+  const int clusters = nc ? atoi(nc) : 1;
+  cfg.gridDim = dim3(2 * (clusters > 0 ? clusters : 1), 1, 1);
   cfg.blockDim = dim3(128, 1, 1);
   cfg.dynamicSmemBytes = (size_t)smem;
   cfg.stream = stream;
@@ -169,11 +176,13 @@ extern "C" int FlashMoeTestPairGemm(const void* W, const void* X, float* D, int 
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   e = cudaLaunchKernelEx(&cfg, pair_gemm_kernel, tm_w, tm_x, D, N, K, boxRows, status);
-  uint32_t hs = 0;
-  if (e == cudaSuccess) e = cudaMemcpyAsync(&hs, status, 4, cudaMemcpyDeviceToHost, stream);
+  uint32_t hs2[2] = {0, 0};
+  if (e == cudaSuccess) e = cudaMemcpyAsync(hs2, status, 8, cudaMemcpyDeviceToHost, stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
   cudaFree(status);
   if (e != cudaSuccess) return (int)e;
+  const uint32_t hs = hs2[0];
+  if (mainLoopNs) *mainLoopNs = hs2[1];
   if (hs != 0) {
     MOE_ERROR_LOG("pair GEMM self-test: a bounded wait ran out (code 0x%x)", hs);
     return (int)cudaErrorUnknown;

@@ -86,8 +86,10 @@ int FlashMoeTestQueueGemm(FlashMoeHandle h, const uint32_t* rowsPerExpertHost, c
  * reference): one cluster of two CTAs computes D[256, N] = W[256, K] * X[N, K]^T with
  * tcgen05.mma.cta_group::2, X arriving in boxes of `boxRows` rows.  W, X bf16 and D fp32 are
  * device pointers; N a multiple of 16 in [16, 256], K a multiple of 64, boxRows a multiple of 8
- * dividing N/2.  Synchronous. */
-int FlashMoeTestPairGemm(const void* W, const void* X, float* D, int N, int K, int boxRows, void* stream);
+ * dividing N/2.  `mainLoopNs` (may be NULL) receives the duration of the MMA issue loop in ns.
+ * Synchronous. */
+int FlashMoeTestPairGemm(const void* W, const void* X, float* D, int N, int K, int boxRows,
+                         unsigned* mainLoopNs, void* stream);
 
 /* The whole layer in one call that allocates nothing (no counterpart in the reference, whose
  * launcher always allocates its scratch in Init, src/hip/launcher/moeKernelLauncher.hip:139-165).

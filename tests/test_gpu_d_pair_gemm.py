@@ -17,7 +17,7 @@ def test_pair_gemm_matches_fp32_product(N, K, box):
     W = torch.randn(256, K, generator=g).to(torch.bfloat16).cuda()
     X = torch.randn(N, K, generator=g).to(torch.bfloat16).cuda()
     D = torch.full((256, N), float("nan"), dtype=torch.float32, device="cuda")
-    code = _lib.lib().FlashMoeTestPairGemm(W.data_ptr(), X.data_ptr(), D.data_ptr(), N, K, box,
+    code = _lib.lib().FlashMoeTestPairGemm(W.data_ptr(), X.data_ptr(), D.data_ptr(), N, K, box, None,
                                            C.c_void_p(torch.cuda.current_stream().cuda_stream))
     _lib.check(code, "FlashMoeTestPairGemm")
     ref = W.float() @ X.float().T
