@@ -42,17 +42,16 @@ constexpr int kWarpTmem = 3;   // allocates / frees TMEM; completion warp in bet
 constexpr int kWarpEpi0 = 4;   // warps 4..11: epilogues and SIMT tasks
 constexpr int kEpiThreads = 256;
 
-constexpr int kStages = 6;
+constexpr int kStages = 4;
 constexpr int kStageA = 128 * FDMOE_TILE_K * 2;  // 16 KB: this CTA's 128 rows of the M operand
-constexpr int kStageB = 128 * FDMOE_TILE_K * 2;  // 16 KB: this CTA's half (up to 128 rows) of the N operand
-constexpr int kStageBytes = kStageA + kStageB;   // 32 KB
+constexpr int kStageB = 128 * FDMOE_TILE_K * 2;  // 16 KB: this CTA's half (up to 128 rows) of one sub-block's N operand
+constexpr int kStageBytes = kStageA + 2 * kStageB;  // 48 KB: two sub-blocks share the M operand
 constexpr int kRing = 3;
-constexpr int kFixBlocks = 2;  // k-blocks of gate weights per stage in a GATEFIX task (2 x 16 KB)
+constexpr int kFixBlocks = 3;  // k-blocks of gate weights per stage in a GATEFIX task (3 x 16 KB)
 constexpr int kPrefetch = 8;  // k-blocks by which the L2 prefetch of weights runs ahead
 constexpr int kDone = 4;  // depth of the hand-off ring to the completion warp
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = 256;
-constexpr int kStg1Pitch = 144;  // FFN1 staging: 32 rows x 64 bf16 (+16 bytes)
 
 // Shared-memory control block of one CTA.  CTAs work in pairs (a cluster of two):
 // the even CTA ("leader") schedules tasks for both and issues the pair's MMAs, so some
@@ -81,9 +80,6 @@ struct __align__(16) SmemCtl {
   uint32_t prof_n;
   uint32_t n_flagged;
   uint32_t pre[16];  // GATED scratch: per-warp totals
-  // FFN2 epilogue: routing weight and destination {element offset of y[token, slot, 0], home rank} of the block's rows
-  float tokw[FDMOE_BLOCK_ROWS];
-  uint2 tokdst[FDMOE_BLOCK_ROWS];
   // The epilogue group runs one task at a time, so the scratch of a GATE task
   // and the store staging of an FFN task share storage.  16-byte aligned: the
   // staging buffer is accessed with 16-byte vector loads and stores.
@@ -106,12 +102,15 @@ struct __align__(16) SmemCtl {
       uint4 xrow[2][FDMOE_MAX_HIDDEN / 8];
       float exact[2][128];
     };
-    // FFN1 epilogue: each half of the epilogue group (four warps) transposes 32 rows of the
-    // block at a time through its staging tile, so that a row leaves as one contiguous piece
-    uint8_t ffn_stage[2][32 * kStg1Pitch];
-    // FFN2 epilogue: per-warp staging of a 32-row x 64-byte chunk (80-byte pitch keeps the 16-byte
-    // accesses of a quarter warp on distinct banks)
-    uint8_t warp_stage[kEpiThreads / 32][32 * 80];
+    struct {
+      // FFN epilogues: per-warp staging of a 32-row chunk (FFN2: 64 bytes per row at an 80-byte pitch,
+      // FFN1: 32 bytes at a 48-byte pitch; the pitches keep 16-byte accesses on distinct banks) ...
+      uint8_t warp_stage[kEpiThreads / 32][32 * 80];
+      // ... and the block's sideband: routing weight and destination {element offset of
+      // y[token, slot, 0], home rank} of every row
+      float tokw[FDMOE_BLOCK_ROWS];
+      uint2 tokdst[FDMOE_BLOCK_ROWS];
+    };
   };
 };
 
@@ -120,8 +119,6 @@ static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA exceeds the sm
 static_assert(offsetof(SmemCtl, xrow) % 16 == 0 && offsetof(SmemCtl, logit_tile) % 16 == 0 && (132 * 4) % 16 == 0,
               "vector accesses to the gate scratch need 16-byte alignment");
 static_assert(offsetof(SmemCtl, warp_stage) % 16 == 0 && (32 * 80) % 16 == 0, "per-warp staging alignment");
-static_assert(offsetof(SmemCtl, ffn_stage) % 16 == 0 && (32 * kStg1Pitch) % 16 == 0 && kStg1Pitch % 16 == 0,
-              "store staging must keep 16-byte alignment for every half and row");
 static_assert(offsetof(SmemCtl, pfull) % 8 == 0 && offsetof(SmemCtl, ring) % 16 == 0 &&
                   offsetof(SmemCtl, tokdst) % 8 == 0,
               "barrier / ring alignment");
@@ -931,33 +928,31 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
-// Barrier over one half of the epilogue group (warps 4h .. 4h+3, 128 threads).
-__device__ __forceinline__ void half_bar(int h) { asm volatile("bar.sync %0, 128;" ::"r"(2 + h) : "memory"); }
-
 // FFN tiles keep the weights as the M operand, so an accumulator holds output features in
-// its lanes and the rows of the block in its columns: thread (q, lane) of either half reads
-// feature lane 32q + lane for 32 rows at a time.  The two halves of the epilogue group take
-// alternate 32-row chunks; each transposes its chunk through a staging tile so that every
-// row leaves as one contiguous piece.
+// its lanes and the rows of the block in its columns: thread (q, lane) of either half of the
+// epilogue group reads feature lane 32q + lane for 32 rows at a time; the two halves take
+// alternate 32-row chunks.
 
 // FFN1 epilogue.  The CTA's 128 weight rows are 4 x (16 gate rows, 16 up rows of the same
 // features), so lanes l and l + 16 of a warp hold gate and up of feature 16q + (l & 15):
 //   act[row, n*128 + cta*64 + f] = silu(gate[f, row]) * up[f, row]
+// Every warp transposes its 16 features x 32 rows through a staging tile of its own (48-byte
+// pitch), so a row's 16 features leave as one 32-byte piece and nothing is exchanged between warps.
 __device__ __forceinline__ void ffn1_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, uint32_t cta, int q,
-                                              int h, int lane, uint32_t le, uint32_t n, uint32_t r0,
+                                              int h, int lane, int ewarp, uint32_t le, uint32_t n, uint32_t r0,
                                               uint32_t rows) {
-  uint8_t* stg = sc.ffn_stage[h];
-  const int gt = q * 32 + lane;  // thread within the half
+  uint8_t* st = sc.warp_stage[ewarp];
   const uint32_t nchunk = (rows + 31u) / 32u;
   uint8_t* actb = reinterpret_cast<uint8_t*>(p.act) +
-                  (((size_t)le * p.cap_rows + r0) * p.I + n * FDMOE_TILE_N1 + cta * 64u) * 2u;
+                  (((size_t)le * p.cap_rows + r0) * p.I + n * FDMOE_TILE_N1 + cta * 64u + (uint32_t)q * 16u) * 2u;
   const uint32_t tbase = taddr + ((uint32_t)(q * 32) << 16);
   const bool lo = lane < 16;
+  const bool skip = (p.debug_flags & 1) != 0;
   for (uint32_t c = (uint32_t)h; c < nchunk; c += 2) {
     uint32_t v[32];
     ptx::tmem_ld_32x32(tbase + c * 32u, v);
     ptx::tmem_ld_wait();
-    float o[16];
+    uint8_t* dst = st + (lo ? 0 : 16) * 48 + (lane & 15) * 2;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       // lanes below 16 keep rows 0..15 and hand their gate of rows 16..31 to the up lane, and vice versa
@@ -965,55 +960,47 @@ __device__ __forceinline__ void ffn1_epilogue(const FdmoeParams& p, SmemCtl& sc,
       const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 16);
       const float g = __uint_as_float(lo ? v[i] : recv);
       const float u = __uint_as_float(lo ? recv : v[16 + i]);
-      o[i] = silu_mul(g, u);
+      *reinterpret_cast<bf16*>(dst + i * 48) = __float2bfloat16_rn(silu_mul(g, u));
     }
-    half_bar(h);  // the previous chunk has left the staging tile
-    {
-      uint8_t* dst = stg + (lo ? 0 : 16) * kStg1Pitch + (q * 16 + (lane & 15)) * 2;
+    __syncwarp();
+    // 32 rows x 32 bytes: lane sends 16 bytes of rows lane / 2 and lane / 2 + 16
 #pragma unroll
-      for (int i = 0; i < 16; ++i) *reinterpret_cast<bf16*>(dst + i * kStg1Pitch) = __float2bfloat16_rn(o[i]);
+    for (int k = 0; k < 2; ++k) {
+      const uint32_t rl = (uint32_t)(lane >> 1) + 16u * (uint32_t)k, row = c * 32u + rl;
+      const uint4 val = *reinterpret_cast<const uint4*>(st + rl * 48 + (lane & 1) * 16);
+      if (row < rows && !skip) *reinterpret_cast<uint4*>(actb + (size_t)row * p.I * 2u + (lane & 1) * 16) = val;
     }
-    half_bar(h);
-    // 32 rows x 128 bytes: thread gt sends 32 bytes of row gt / 4
-    const uint32_t row = c * 32u + (uint32_t)(gt >> 2);
-    if (row < rows && !(p.debug_flags & 1)) {
-      const uint4* src = reinterpret_cast<const uint4*>(stg + (gt >> 2) * kStg1Pitch + (gt & 3) * 32);
-      uint4* dst = reinterpret_cast<uint4*>(actb + (size_t)row * p.I * 2u + (gt & 3) * 32);
-      const uint4 a = src[0], b = src[1];
-      dst[0] = a;
-      dst[1] = b;
-    }
+    __syncwarp();
   }
 }
 
 // FFN2 epilogue: y[token, slot, n*256 + cta*128 + f] = D[f, row] * routing weight of the row,
-// stored on the token's home rank.  sc.tokw holds the block's routing weights, sc.tokdst the
+// stored on the token's home rank, for the `rows` rows of a sub-block that starts `roff` rows into
+// its block.  sc.tokw holds the block's routing weights, sc.tokdst the
 // element offset of (token, slot, 0) in the home rank's staging area and the home rank.  Every
 // warp transposes its 32 features x 32 rows through a staging tile of its own, so nothing is
 // exchanged between warps.
 __device__ __forceinline__ void ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, uint32_t cta, int q,
-                                              int h, int lane, int ewarp, uint32_t n, uint32_t rows) {
+                                              int h, int lane, int ewarp, uint32_t n, uint32_t roff,
+                                              uint32_t rows) {
   const uint32_t nchunk = (rows + 31u) / 32u;
   const uint32_t tbase = taddr + ((uint32_t)(q * 32) << 16);
   const uint32_t col0 = n * FDMOE_TILE_N2 + cta * 128u;  // first of this CTA's 128 features
   const bool skip = (p.debug_flags & 1) != 0;
   uint8_t* st = sc.warp_stage[ewarp];
-  long long c_ld = 0, c_a = 0, c_b = 0;
   for (uint32_t c = (uint32_t)h; c < nchunk; c += 2) {
     uint32_t v[32];
-    const long long k0 = clock64();
     ptx::tmem_ld_32x32(tbase + c * 32u, v);
     // lane i prepares row 32c + i: where this CTA's 256-byte piece of it goes and its routing weight
     const uint32_t myrow = c * 32u + (uint32_t)lane;
     unsigned long long mydst = 0ull;
     float myw = 0.f;
     if (myrow < rows && !skip) {
-      const uint2 d = sc.tokdst[myrow];  // {element offset of the row's slot, home rank}
+      const uint2 d = sc.tokdst[roff + myrow];  // {element offset of the row's slot, home rank}
       mydst = reinterpret_cast<unsigned long long>(reinterpret_cast<bf16*>(p.peers[d.y].ystage) + (size_t)d.x + col0);
-      myw = sc.tokw[myrow];
+      myw = sc.tokw[roff + myrow];
     }
     ptx::tmem_ld_wait();
-    const long long k1 = clock64();
     // transpose this warp's 32 features x 32 rows through its own staging tile: a row's 32 features
     // (64 bytes) then leave as four 16-byte stores, eight rows per store instruction
 #pragma unroll
@@ -1022,7 +1009,6 @@ __device__ __forceinline__ void ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc,
       *reinterpret_cast<bf16*>(st + i * 80 + lane * 2) = __float2bfloat16_rn(__uint_as_float(v[i]) * wi);
     }
     __syncwarp();
-    const long long k2 = clock64();
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const int r = (lane >> 2) + 8 * k;
@@ -1031,12 +1017,7 @@ __device__ __forceinline__ void ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc,
       if (dr != 0ull) *reinterpret_cast<uint4*>(dr + (unsigned long long)(q * 64 + (lane & 3) * 16)) = val;
     }
     __syncwarp();
-    const long long k3 = clock64();
-    c_ld += k1 - k0;
-    c_a += k2 - k1;
-    c_b += k3 - k2;
   }
-  if (p.prof && q == 0 && h == 0 && lane == 0) prof_event(p, sc, 250u, (uint32_t)c_ld, (uint32_t)c_a, (uint32_t)c_b);
 }
 
 // COMBINE streams the K weighted rows of each token of a group through the
@@ -1101,7 +1082,7 @@ __device__ __noinline__ bool pack_loads(const FdmoeParams& p, SmemCtl& sc, uint8
 // TMA-warp side of a pair tile (one thread per CTA): per k-block this CTA's 128 rows of the M
 // operand and its half of the N operand, completion counted on the leader's barrier.
 //   GATE  M: this CTA's token tile            N: 64 rows of the gate weights
-//   FFN1  M: 4 x (16 gate + 16 up rows)       N: rows [r0 + cta*nh, +nh) of the expert's packed rows
+//   FFN1  M: 4 x (16 gate + 16 up rows)       N: this CTA's half of each sub-block of the expert's packed rows
 //   FFN2  M: 128 rows of W2                   N: the same rows of the expert's activations
 // (Inlined into the kernel on purpose: there the parameter block is read through the constant bank; behind
 // a call it would be reached through a generic pointer, which costs hundreds of cycles per access.)
@@ -1113,8 +1094,12 @@ __device__ __forceinline__ bool pair_loads(const FdmoeParams& p, SmemCtl& sc, ui
   const uint32_t e = (p.debug_flags & 32) ? 0u : (t.a >> 8) & 0xfffu, n = (p.debug_flags & 32) ? 0u : t.a >> 20;
   const bool f1 = kind == FDMOE_TASK_FFN1, gt = kind == FDMOE_TASK_GATE;
   const uint32_t nkb = (uint32_t)((f1 || gt) ? p.H : p.I) / FDMOE_TILE_K;
-  const uint32_t nh = gt ? 0u : (((t.c + 15u) & ~15u) >> 1);  // rows of the N operand held by this CTA
-  const int32_t brow = gt ? 0 : (int32_t)(e * (uint32_t)p.cap_rows + ((p.debug_flags & 32) ? 0u : t.b) + cta * nh);
+  // rows of the two sub-blocks' N operands held by this CTA (half of each MMA extent)
+  uint32_t n0 = 0u, n1 = 0u;
+  if (!gt) fdmoe_split_rows(t.c, &n0, &n1);
+  const uint32_t nh0 = ((n0 + 15u) & ~15u) >> 1, nh1 = ((n1 + 15u) & ~15u) >> 1;
+  const uint32_t row0 = e * (uint32_t)p.cap_rows + ((p.debug_flags & 32) ? 0u : t.b);
+  const int32_t brow0 = (int32_t)(row0 + cta * nh0), brow1 = (int32_t)(row0 + n0 + cta * nh1);
   // GATE boxes are clamped to the tensor extents, and a box that lies wholly outside is not requested at all
   const bool gate_b = cta * 64u < (uint32_t)p.E;  // this CTA's 64 gate-weight rows exist (at least partly)
   const bool gate_a = (2u * t.b + cta) * (uint32_t)p.gate_rows < (uint32_t)p.T;  // this CTA's token tile exists
@@ -1127,9 +1112,11 @@ __device__ __forceinline__ bool pair_loads(const FdmoeParams& p, SmemCtl& sc, ui
     const uint32_t wboxes = 64 < p.E ? 2u : 1u;
     pair_bytes = (tiles * (uint32_t)min(p.gate_rows, p.T) + wboxes * (uint32_t)min(64, p.E)) * FDMOE_TILE_K * 2u;
   } else {
-    pair_bytes = 2u * (128u + nh) * FDMOE_TILE_K * 2u;
+    pair_bytes = 2u * (128u + nh0 + nh1) * FDMOE_TILE_K * 2u;
   }
-  const FdmoeTensorMap* bmap = gt ? nullptr : (f1 ? p.tm_packed_rows : p.tm_act_rows) + (nh / 8u - 1u);
+  const FdmoeTensorMap* const bmaps = f1 ? p.tm_packed_rows : p.tm_act_rows;  // entry i: box of 8 (i + 1) rows
+  const FdmoeTensorMap* const bmap0 = gt ? nullptr : bmaps + (nh0 / 8u - 1u);
+  const FdmoeTensorMap* const bmap1 = nh1 ? bmaps + (nh1 / 8u - 1u) : nullptr;
   const uint32_t dbg = (uint32_t)p.debug_flags;
   const FdmoeTensorMap* const map_w13 = &p.tm_w13;
   const FdmoeTensorMap* const map_w2 = &p.tm_w2;
@@ -1160,14 +1147,15 @@ __device__ __forceinline__ bool pair_loads(const FdmoeParams& p, SmemCtl& sc, ui
       ptx::tma_load_5d_pair(sa, map_w13, full0, kx, 0, 0, grp, (int32_t)e);
       // The weights come from HBM: ask L2 for them kPrefetch k-blocks ahead, so that the
       // shared-memory stages only have to cover the L2 latency.
-      if (kb + kPrefetch < nkb && !(dbg & 16u)) ptx::tma_prefetch_l2_5d(map_w13, kx + kPrefetch * FDMOE_TILE_K, 0, 0, grp, (int32_t)e);
+      if (kb + kPrefetch < nkb && (dbg & 16u)) ptx::tma_prefetch_l2_5d(map_w13, kx + kPrefetch * FDMOE_TILE_K, 0, 0, grp, (int32_t)e);
     } else {
       const int32_t wrow = (int32_t)(e * (uint32_t)p.H + n * FDMOE_TILE_N2 + cta * 128u);
       ptx::tma_load_2d_pair(sa, map_w2, full0, kx, wrow);
-      if (kb + kPrefetch < nkb && !(dbg & 16u)) ptx::tma_prefetch_l2_2d(map_w2, kx + kPrefetch * FDMOE_TILE_K, wrow);
+      if (kb + kPrefetch < nkb && (dbg & 16u)) ptx::tma_prefetch_l2_2d(map_w2, kx + kPrefetch * FDMOE_TILE_K, wrow);
     }
-    // this CTA's half of the block's rows in one box (descriptor chosen by its height)
-    ptx::tma_load_2d_pair(sb, bmap, full0, kx, brow);
+    // this CTA's half of each sub-block's rows in one box (descriptor chosen by its height)
+    ptx::tma_load_2d_pair(sb, bmap0, full0, kx, brow0);
+    if (nh1) ptx::tma_load_2d_pair(sb + kStageB, bmap1, full0, kx, brow1);
     cur.w_issue += (uint64_t)(clock64() - tq);
   }
   return true;
@@ -1436,15 +1424,20 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         if (kind == FDMOE_TASK_EXIT) break;
         if (is_pair_task(kind) && cta == 0u) {
           const uint32_t nkb = (kind == FDMOE_TASK_FFN2) ? nkb2 : nkb1;
-          const uint32_t ncols = (kind == FDMOE_TASK_GATE) ? 128u : ((t.c + 15u) & ~15u);
-          const uint32_t idesc = ptx::make_idesc_bf16(256, ncols);
-          const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
-          ++tile_it;
+          // one accumulator per sub-block (GATE: one, 128 columns)
+          uint32_t n0 = 128u, n1 = 0u;
+          if (kind != FDMOE_TASK_GATE) fdmoe_split_rows(t.c, &n0, &n1);
+          const uint32_t idesc0 = ptx::make_idesc_bf16(256, (n0 + 15u) & ~15u);
+          const uint32_t idesc1 = ptx::make_idesc_bf16(256, (n1 + 15u) & ~15u);
+          const uint32_t acc0 = tile_it & 1u, aph0 = (tile_it >> 1) & 1u;
+          const uint32_t acc1 = (tile_it + 1u) & 1u, aph1 = ((tile_it + 1u) >> 1) & 1u;
+          tile_it += n1 ? 2u : 1u;
           const long long ta = clock64();
-          if (!wait_bar(p, sc, &sc.tmem_empty[acc], aph ^ 1u, FDMOE_ERR_TIMEOUT_TMEM)) break;
+          if (!wait_bar(p, sc, &sc.tmem_empty[acc0], aph0 ^ 1u, FDMOE_ERR_TIMEOUT_TMEM)) break;
+          if (n1 && !wait_bar(p, sc, &sc.tmem_empty[acc1], aph1 ^ 1u, FDMOE_ERR_TIMEOUT_TMEM)) break;
           w_acc += (uint64_t)(clock64() - ta);
           ptx::tcgen05_fence_after();
-          const uint32_t d_tmem = tmem_base + acc * kAccCols;
+          const uint32_t d0 = tmem_base + acc0 * kAccCols, d1 = tmem_base + acc1 * kAccCols;
           bool ok = true;
           for (uint32_t kb = 0; kb < nkb; ++kb, ++pit) {
             const uint32_t s = pit % kStages, sph = (pit / kStages) & 1u;
@@ -1456,11 +1449,13 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
             ptx::tcgen05_fence_after();
             const uint32_t sa = ptx::smem_u32(stage + s * kStageBytes);
             const uint64_t da = ptx::make_smem_desc_sw128(sa);
-            const uint64_t db = ptx::make_smem_desc_sw128(sa + kStageA);
+            const uint64_t db0 = ptx::make_smem_desc_sw128(sa + kStageA);
+            const uint64_t db1 = ptx::make_smem_desc_sw128(sa + kStageA + kStageB);
 #pragma unroll
             for (uint32_t k4 = 0; k4 < FDMOE_TILE_K / 16; ++k4) {
               // +32 bytes per 16-element k step inside the 128-byte swizzle row
-              ptx::umma_bf16_pair(d_tmem, da + k4 * 2u, db + k4 * 2u, idesc, (kb | k4) != 0u);
+              ptx::umma_bf16_pair(d0, da + k4 * 2u, db0 + k4 * 2u, idesc0, (kb | k4) != 0u);
+              if (n1) ptx::umma_bf16_pair(d1, da + k4 * 2u, db1 + k4 * 2u, idesc1, (kb | k4) != 0u);
             }
             // frees the stage in both CTAs when the MMAs have read it
             const uint32_t eb = ptx::smem_u32(&sc.pempty[s]);
@@ -1469,9 +1464,14 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
             w_issue += (uint64_t)(clock64() - ti);
           }
           if (!ok) break;
-          const uint32_t fb = ptx::smem_u32(&sc.tmem_full[acc]);
-          ptx::umma_commit_pair(fb);
-          ptx::umma_commit_pair(ptx::map_to_cta(fb, 1u));
+          const uint32_t fb0 = ptx::smem_u32(&sc.tmem_full[acc0]);
+          ptx::umma_commit_pair(fb0);
+          ptx::umma_commit_pair(ptx::map_to_cta(fb0, 1u));
+          if (n1) {
+            const uint32_t fb1 = ptx::smem_u32(&sc.tmem_full[acc1]);
+            ptx::umma_commit_pair(fb1);
+            ptx::umma_commit_pair(ptx::map_to_cta(fb1, 1u));
+          }
         }
         ring_release(sc, cta, r);
       }
@@ -1511,28 +1511,39 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       } else if (kind == FDMOE_TASK_GATEFIX) {
         if (!gatefix_task<S>(p, sc, stage, stage_it, etid, ewarp, lane, j, rows)) break;
       } else if (kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2) {
-        const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
-        ++tile_it;
         if (kind == FDMOE_TASK_FFN2) {
           // sideband of the block's rows, fetched while the tile is still being computed
-          if ((uint32_t)etid < rows) {
-            const uint4 mraw = ld_cg_u4(&me.meta[(size_t)e * p.cap_rows + j + etid]);
-            sc.tokw[etid] = __uint_as_float(mraw.z);
+          for (uint32_t i = (uint32_t)etid; i < rows; i += kEpiThreads) {
+            const uint4 mraw = ld_cg_u4(&me.meta[(size_t)e * p.cap_rows + j + i]);
+            sc.tokw[i] = __uint_as_float(mraw.z);
             // element offset of y[token, slot, 0] on the home rank (below 2^32: the launcher checks the size)
-            sc.tokdst[etid] = make_uint2((mraw.x * (uint32_t)p.K + (mraw.y & 0xffu)) * (uint32_t)p.H, mraw.y >> 8);
+            sc.tokdst[i] = make_uint2((mraw.x * (uint32_t)p.K + (mraw.y & 0xffu)) * (uint32_t)p.H, mraw.y >> 8);
           }
         }
-        if (!epi_vote_all(wait_bar_warp(p, sc, &sc.tmem_full[acc], aph, FDMOE_ERR_TIMEOUT_TMEM))) break;
-        if (p.prof && etid == 0) pt1 = prof_now();
-        ptx::tcgen05_fence_after();
-        const uint32_t taddr = tmem_base + acc * kAccCols;
-        if (kind == FDMOE_TASK_FFN1)
-          ffn1_epilogue(p, sc, taddr, cta, q, h, lane, e, n, j, rows);
-        else
-          ffn2_epilogue(p, sc, taddr, cta, q, h, lane, ewarp, n, rows);
-        ptx::tcgen05_fence_before();
-        __syncwarp();
-        if (lane == 0) acc_release(sc, cta, acc);
+        uint32_t nsub[2];
+        fdmoe_split_rows(rows, &nsub[0], &nsub[1]);
+        bool ok = true;
+        uint32_t roff = 0u;
+        for (int sb = 0; sb < 2 && ok; ++sb) {
+          if (nsub[sb] == 0u) break;
+          // sub-block sb was accumulated in the next accumulator of the sequence
+          const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
+          ++tile_it;
+          ok = epi_vote_all(wait_bar_warp(p, sc, &sc.tmem_full[acc], aph, FDMOE_ERR_TIMEOUT_TMEM));
+          if (!ok) break;
+          if (p.prof && etid == 0 && sb == 0) pt1 = prof_now();
+          ptx::tcgen05_fence_after();
+          const uint32_t taddr = tmem_base + acc * kAccCols;
+          if (kind == FDMOE_TASK_FFN1)
+            ffn1_epilogue(p, sc, taddr, cta, q, h, lane, ewarp, e, n, j + roff, nsub[sb]);
+          else
+            ffn2_epilogue(p, sc, taddr, cta, q, h, lane, ewarp, n, roff, nsub[sb]);
+          ptx::tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) acc_release(sc, cta, acc);
+          roff += nsub[sb];
+        }
+        if (!ok) break;
         const uint32_t pta = (p.prof && etid == 0) ? prof_now() : 0u;
 
         // The tile's stores are issued.  Dependency counting, successor pushes and

@@ -13,9 +13,11 @@ enum {
   FDMOE_MAX_EXPERTS = 128,
   FDMOE_MAX_HIDDEN = 4096,  // a token row is staged in shared memory by the exact gate path
   // FFN tiles are computed by a pair of CTAs with the weights as the M operand (256 weight rows,
-  // 128 per CTA) and up to 256 rows of one expert as the N operand (split between the CTAs):
+  // 128 per CTA) and rows of one expert as the N operand (each MMA's rows split between the CTAs).
+  // A tile covers a "row block" of up to 512 rows as one or two sub-blocks of up to 256 rows (one
+  // MMA extent each) that share the weight operand.
   FDMOE_TILE_M = 128,    // granule of an expert's row buffer (capacity, per-block counters)
-  FDMOE_BLOCK_ROWS = 256,  // most rows of one expert in one tile (a "row block")
+  FDMOE_BLOCK_ROWS = 512,  // most rows of one expert in one tile
   FDMOE_TILE_N1 = 128,   // FFN1: activation columns per pair tile (256 weight rows: gate + up)
   FDMOE_TILE_N2 = 256,   // FFN2: hidden columns per pair tile
   FDMOE_TILE_K = 64,     // one 128-byte swizzle atom of bf16 per stage
@@ -175,3 +177,18 @@ int fdmoe_cast_bf16_to_f32(const void* src, float* dst, uint64_t n, void* stream
 #ifdef __cplusplus
 }
 #endif
+
+// Sub-blocks of a row block of `rows` rows (1..512): n0 rows (a multiple of 16 unless it is the
+// only sub-block) followed by n1 rows (0 if the block fits one MMA extent of 256 rows).
+#if defined(__CUDACC__)
+__host__ __device__
+#endif
+static inline void fdmoe_split_rows(uint32_t rows, uint32_t* n0, uint32_t* n1) {
+  if (rows <= 256u) {
+    *n0 = rows;
+    *n1 = 0u;
+  } else {
+    *n0 = ((rows + 1u) / 2u + 15u) & ~15u;
+    *n1 = rows - *n0;
+  }
+}
