@@ -51,14 +51,14 @@ struct Geometry {
 };
 
 // Slots of a rank's task queue: at least every task one launch can publish there, so that a
-// slot is never reused within a launch.  Tile tasks of the rank's experts (per row block), COMBINE tasks (at
+// slot is never reused within a launch.  Tile tasks of the rank's experts, COMBINE tasks (at
 // most max_tokens / combine_group + one wave of `grid`), GATED, this rank's GATE tasks (>= 32
 // tokens each), PACK pieces (FDMOE_PACK_ROWS rows, one ragged piece per expert) and GATEFIX
 // tasks (two tokens each, every token in the worst case), plus EXIT tickets of every worker.
 inline uint32_t QueueCapacity(const Geometry& g, int grid) {
   const uint64_t rows_max = std::min<uint64_t>((uint64_t)g.max_tokens_sum * g.K, (uint64_t)g.El * g.cap_rows);
-  const uint64_t blocks = rows_max / (FDMOE_BLOCK_ROWS / 2) + g.El;  // balanced blocks hold more than half a block
-  const uint64_t tasks = blocks * (g.I / FDMOE_TILE_N1 + g.H / FDMOE_TILE_N2) +
+  const uint64_t mtiles = rows_max / FDMOE_TILE_M + g.El;
+  const uint64_t tasks = mtiles * (g.I / FDMOE_TILE_N1 + g.H / FDMOE_TILE_N2) +
                          (uint64_t)g.max_tokens_max / std::max(1, g.combine_group) + grid + 64 +
                          (uint64_t)g.max_tokens_max / 32 + (uint64_t)g.max_tokens_max * g.K / FDMOE_PACK_ROWS + g.E +
                          (uint64_t)g.max_tokens_max / 2 + 1024;
@@ -94,7 +94,6 @@ inline ArenaLayout MakeLayout(const Geometry& g) {
   return L;
 }
 
-// (see MakeTensorMap / MakeTensorMap3 below)
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -128,51 +127,6 @@ inline cudaError_t MakeTensorMap(EncodeTiledFn enc, FdmoeTensorMap* out, const v
     return cudaErrorInvalidValue;
   }
   return cudaSuccess;
-}
-
-// The FFN1 weights of all local experts, [El][2][I][H] bf16 (gate rows, then up rows), as a 5-D
-// tensor {H, row within a group of 16, half, group, expert}.  One box is 64 columns x 16 rows x
-// both halves x 4 groups: in shared memory four times (16 gate rows, then the up rows of the
-// same 16 features), 128 rows of 128 bytes.
-inline cudaError_t MakeTensorMapW13(EncodeTiledFn enc, FdmoeTensorMap* out, const void* base, uint64_t experts,
-                                    uint64_t inter, uint64_t hidden) {
-  const cuuint64_t dims[5] = {hidden, 16, 2, inter / 16, experts};
-  const cuuint64_t strides[4] = {hidden * 2, inter * hidden * 2, 16 * hidden * 2, 2 * inter * hidden * 2};
-  const cuuint32_t box[5] = {FDMOE_TILE_K, 16, 2, 4, 1};
-  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-  const CUresult r = enc(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5,
-                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    MOE_ERROR_LOG("cuTensorMapEncodeTiled (5-D) failed with %d", (int)r);
-    return cudaErrorInvalidValue;
-  }
-  return cudaSuccess;
-}
-
-// Descriptors of the row-block operands (FDMOE_ROW_MAPS per matrix, box heights 8, 16, ..., 128).
-enum { FDMOE_ROW_MAPS = 16 };
-struct RowMaps {
-  FdmoeTensorMap packed[FDMOE_ROW_MAPS];
-  FdmoeTensorMap act[FDMOE_ROW_MAPS];
-};
-
-// The launch-independent TMA descriptors of one rank: those passed as kernel parameters are written
-// into *p, those of the row-block operands into *rows (host memory; the caller copies it to the
-// device and points p->tm_packed_rows / tm_act_rows at the copies).
-inline cudaError_t MakeStaticMaps(EncodeTiledFn enc, FdmoeParams* p, RowMaps* rows, const Geometry& g,
-                                  const void* packed, const void* act, const void* w13, const void* w2,
-                                  const void* gate) {
-  const uint64_t exp_rows = (uint64_t)g.El * g.cap_rows;
-  cudaError_t e;
-  for (uint32_t i = 0; i < FDMOE_ROW_MAPS; ++i) {
-    if ((e = MakeTensorMap(enc, &rows->packed[i], packed, exp_rows, g.H, 8 * (i + 1))) != cudaSuccess) return e;
-    if ((e = MakeTensorMap(enc, &rows->act[i], act, exp_rows, g.I, 8 * (i + 1))) != cudaSuccess) return e;
-  }
-  if ((e = MakeTensorMapW13(enc, &p->tm_w13, w13, g.El, g.I, g.H)) != cudaSuccess) return e;
-  if ((e = MakeTensorMap(enc, &p->tm_w2, w2, (uint64_t)g.El * g.H, g.I, 128)) != cudaSuccess) return e;
-  return MakeTensorMap(enc, &p->tm_gate, gate, (uint64_t)g.E, g.H, (uint32_t)std::min(64, g.E));
 }
 
 }  // namespace fdmoe

@@ -92,7 +92,6 @@ class MoeKernelLauncher final : public moe::IMoeKernelLauncher {
   float* topk_w_ = nullptr;
   int32_t* send_src_ = nullptr;  // this rank's send lists [E][maxTokens]
   int32_t* send_dst_ = nullptr;
-  RowMaps* row_maps_ = nullptr;  // device copy of the row-block TMA descriptors
   uint32_t* status_host_ = nullptr;
   uint32_t* status_dev_ = nullptr;
   // fp32 I/O mode: bf16 copies of the weights and token staging
@@ -112,7 +111,7 @@ void MoeKernelLauncher::FreeAll() {
   for (int r = 0; r < (int)peer_bases_.size(); ++r)
     if (r != rank_ && peer_bases_[r]) cudaIpcCloseMemHandle(peer_bases_[r]);
   peer_bases_.clear();
-  void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, send_src_, send_dst_, row_maps_, gate_bf16_, w13_bf16_, w2_bf16_,
+  void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, send_src_, send_dst_, gate_bf16_, w13_bf16_, w2_bf16_,
                   tok_bf16_, out_bf16_, host_in_dev_, host_out_dev_, prof_, debug_logits_, stuck_};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -121,7 +120,6 @@ void MoeKernelLauncher::FreeAll() {
   topk_idx_ = nullptr;
   topk_w_ = nullptr;
   send_src_ = send_dst_ = nullptr;
-  row_maps_ = nullptr;
   gate_bf16_ = w13_bf16_ = w2_bf16_ = tok_bf16_ = out_bf16_ = host_in_dev_ = host_out_dev_ = nullptr;
   prof_ = nullptr;
   debug_logits_ = nullptr;
@@ -213,12 +211,6 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   g_.cap_rows = (int)AlignUp((size_t)std::max<int64_t>(g_.max_tokens_sum, 1), FDMOE_TILE_M);
   g_.MT = g_.cap_rows / FDMOE_TILE_M;
   g_.combine_group = std::max(1, EnvInt("FLASHMOE_COMBINE_GROUP", 16));
-  if ((uint64_t)g_.max_tokens_max * g_.K * g_.H >= (1ull << 32)) {
-    MOE_ERROR_LOG("maxTokens * topK * hidden = %llu elements of weighted rows per rank: the kernel addresses them with 32 bits",
-                  (unsigned long long)g_.max_tokens_max * g_.K * g_.H);
-    FreeAll();
-    return cudaErrorUnknown;
-  }
   g_.queue_cap = QueueCapacity(g_, grid_);
   layout_ = MakeLayout(g_);
 
@@ -288,14 +280,12 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
     FreeAll();
     return cudaErrorUnknown;
   }
-  {
-    RowMaps rows;
-    CUDA_ERROR_CHECK(MakeStaticMaps(enc, &params_, &rows, g_, arena_ + layout_.packed, act_, w13_dev, w2_dev, gate_dev));
-    CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&row_maps_), sizeof(RowMaps)));
-    CUDA_ERROR_CHECK(cudaMemcpy(row_maps_, &rows, sizeof(RowMaps), cudaMemcpyHostToDevice));
-    params_.tm_packed_rows = row_maps_->packed;
-    params_.tm_act_rows = row_maps_->act;
-  }
+  const uint64_t exp_rows = (uint64_t)g_.El * g_.cap_rows;
+  CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_packed, arena_ + layout_.packed, exp_rows, g_.H, 128));
+  CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_w13, w13_dev, (uint64_t)g_.El * 2 * g_.I, g_.H, 128));
+  CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_act, act_, exp_rows, g_.I, 128));
+  CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_w2, w2_dev, (uint64_t)g_.El * g_.H, g_.I, 256));
+  CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_gate, gate_dev, (uint64_t)g_.E, g_.H, std::min(128, g_.E)));
   encode_ = enc;
   for (int r = 0; r < world; ++r) {
     uint8_t* b = static_cast<uint8_t*>(peer_bases_[r]);
@@ -505,14 +495,10 @@ cudaError_t MoeKernelLauncher::TestQueueGemm(const uint32_t* rowsPerExpert, cons
     for (uint32_t r = 0; r < rows; ++r) meta[r] = FdmoeRowMeta{(int32_t)(row0 + r), rank_ << 8, 1.0f, 0};
     CUDA_ERROR_CHECK(cudaMemcpy(arena_ + layout_.meta + (size_t)e * g_.cap_rows * sizeof(FdmoeRowMeta), meta.data(),
                                 rows * sizeof(FdmoeRowMeta), cudaMemcpyHostToDevice));
-    // row blocks as the layer forms them: as few blocks of at most 256 rows as possible, equal in
-    // size up to the 16-row granule of the tile's N extent
-    const uint32_t nblk = (rows + FDMOE_BLOCK_ROWS - 1) / FDMOE_BLOCK_ROWS;
-    const uint32_t rpb = ((rows + nblk - 1) / nblk + 15u) & ~15u;
-    for (uint32_t n = 0; n < nt2; ++n)
-      for (uint32_t j = 0; j < nblk; ++j)
-        tasks.push_back(FdmoeSlot{0, (uint32_t)FDMOE_TASK_FFN2 | ((uint32_t)e << 8) | (n << 20), j * rpb,
-                                  std::min<uint32_t>(rpb, rows - j * rpb)});
+    for (uint32_t j = 0; j * 128 < rows; ++j)
+      for (uint32_t n = 0; n < nt2; ++n)
+        tasks.push_back(FdmoeSlot{0, (uint32_t)FDMOE_TASK_FFN2 | ((uint32_t)e << 8) | (n << 20), j,
+                                  std::min<uint32_t>(128, rows - j * 128)});
     row0 += rows;
   }
   if (tasks.size() + 1024 > g_.queue_cap) return cudaErrorInvalidValue;
@@ -522,8 +508,7 @@ cudaError_t MoeKernelLauncher::TestQueueGemm(const uint32_t* rowsPerExpert, cons
   void* saved_y = params_.peers[rank_].ystage;
   params_.K = 1;
   params_.peers[rank_].ystage = out;
-  // both CTAs of a pair report a finished tile
-  const cudaError_t e = LaunchBf16(nullptr, nullptr, 0, stream, 2, (uint32_t)tasks.size() * 2u);
+  const cudaError_t e = LaunchBf16(nullptr, nullptr, 0, stream, 2, (uint32_t)tasks.size());
   params_.K = saved_k;
   params_.peers[rank_].ystage = saved_y;
   return e;

@@ -43,9 +43,9 @@ constexpr int kWarpEpi0 = 4;   // warps 4..11: epilogues and SIMT tasks
 constexpr int kEpiThreads = 256;
 
 constexpr int kStages = 4;
-constexpr int kStageA = 128 * FDMOE_TILE_K * 2;  // 16 KB: this CTA's 128 rows of the M operand
-constexpr int kStageB = 128 * FDMOE_TILE_K * 2;  // 16 KB: this CTA's half (up to 128 rows) of one sub-block's N operand
-constexpr int kStageBytes = kStageA + 2 * kStageB;  // 48 KB: two sub-blocks share the M operand
+constexpr int kStageA = FDMOE_TILE_M * FDMOE_TILE_K * 2;  // 16 KB
+constexpr int kStageB = 256 * FDMOE_TILE_K * 2;           // 32 KB
+constexpr int kStageBytes = kStageA + kStageB;            // 48 KB
 constexpr int kRing = 3;
 constexpr int kFixBlocks = 3;  // k-blocks of gate weights per stage in a GATEFIX task (3 x 16 KB)
 constexpr int kPrefetch = 8;  // k-blocks by which the L2 prefetch of weights runs ahead
@@ -53,33 +53,31 @@ constexpr int kDone = 4;  // depth of the hand-off ring to the completion warp
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = 256;
 
-// Shared-memory control block of one CTA.  CTAs work in pairs (a cluster of two):
-// the even CTA ("leader") schedules tasks for both and issues the pair's MMAs, so some
-// barriers are only used in the leader's copy and are signalled by the partner remotely.
-struct __align__(16) SmemCtl {
-  // Operand stages are used by two kinds of task with separate barrier sets:
-  // pair tiles (filled by both CTAs' TMA threads, read by the leader's MMAs) ...
-  uint64_t pfull[kStages];    // leader's copy only: both CTAs' loads of the stage have landed (one arrival: the leader's)
-  uint64_t pempty[kStages];   // the MMAs have read this CTA's stage (tcgen05.commit from the leader)
-  // ... and single-CTA tasks whose stages are read by the epilogue warps (GATEFIX, PACK, COMBINE)
+struct __align__(64) SmemCtl {
   uint64_t full_bar[kStages];
   uint64_t empty_bar[kStages];
-  uint64_t tmem_full[2];      // accumulator complete (commit from the leader, in both CTAs)
-  uint64_t tmem_empty[2];     // leader's copy only: the epilogue warps of both CTAs have drained it
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
   uint64_t ring_full[kRing];
-  uint64_t ring_empty[2][kRing];  // leader's copy only: [c][r] = slot r of CTA c's ring is consumed
-  alignas(16) FdmoeSlot ring[kRing];
+  uint64_t ring_empty[kRing];
+  FdmoeSlot ring[kRing];
   uint64_t done_full[kDone];   // epilogue -> completion warp: a tile's stores are issued
   uint64_t done_empty[kDone];
-  alignas(16) FdmoeSlot done_ring[kDone];
+  FdmoeSlot done_ring[kDone];
   uint32_t tmem_base;
   volatile uint32_t abort;
+  volatile uint32_t skip_done;  // COMBINE / GATEFIX tasks finished by the epilogue warps
   int32_t flag;
   uint32_t q_t0;
   uint32_t q_total;
   uint32_t prof_n;
   uint32_t n_flagged;
-  uint32_t pre[16];  // GATED scratch: per-warp totals
+  uint32_t pre[16];  // flush scratch: per-warp totals
+  // Copy of the kernel parameters for the task bodies that are compiled as separate functions:
+  // there the parameter block is only reachable through a generic pointer, and every access to
+  // the constant bank through one costs on the order of a hundred cycles; shared memory does not.
+  // (TMA descriptors are always taken from the original.)
+  FdmoeParams params;
   // The epilogue group runs one task at a time, so the scratch of a GATE task
   // and the store staging of an FFN task share storage.  16-byte aligned: the
   // staging buffer is accessed with 16-byte vector loads and stores.
@@ -102,15 +100,9 @@ struct __align__(16) SmemCtl {
       uint4 xrow[2][FDMOE_MAX_HIDDEN / 8];
       float exact[2][128];
     };
-    struct {
-      // FFN epilogues: per-warp staging of a 32-row chunk (FFN2: 64 bytes per row at an 80-byte pitch,
-      // FFN1: 32 bytes at a 48-byte pitch; the pitches keep 16-byte accesses on distinct banks) ...
-      uint8_t warp_stage[kEpiThreads / 32][32 * 80];
-      // ... and the block's sideband: routing weight and destination {element offset of
-      // y[token, slot, 0], home rank} of every row
-      float tokw[FDMOE_BLOCK_ROWS];
-      uint2 tokdst[FDMOE_BLOCK_ROWS];
-    };
+    // FFN epilogues: per-warp staging of a 32-row x 64-byte chunk (80-byte pitch
+    // keeps the 16-byte accesses of a quarter warp on distinct banks)
+    uint8_t store_stage[kEpiThreads / 32][32 * 80];
   };
 };
 
@@ -118,11 +110,9 @@ constexpr int kSmemBytes = kStages * kStageBytes + (int)sizeof(SmemCtl) + 1024;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA exceeds the sm_100 limit");
 static_assert(offsetof(SmemCtl, xrow) % 16 == 0 && offsetof(SmemCtl, logit_tile) % 16 == 0 && (132 * 4) % 16 == 0,
               "vector accesses to the gate scratch need 16-byte alignment");
-static_assert(offsetof(SmemCtl, warp_stage) % 16 == 0 && (32 * 80) % 16 == 0, "per-warp staging alignment");
-static_assert(offsetof(SmemCtl, pfull) % 8 == 0 && offsetof(SmemCtl, ring) % 16 == 0 &&
-                  offsetof(SmemCtl, tokdst) % 8 == 0,
-              "barrier / ring alignment");
-static_assert(FDMOE_MAX_TOPK * 2048 * 2 <= kStageBytes, "a COMBINE stage holds K pieces of 2048 columns");
+static_assert(offsetof(SmemCtl, store_stage) % 16 == 0 && (32 * 80) % 16 == 0 && 80 % 16 == 0,
+              "store staging must keep 16-byte alignment for every warp and row");
+static_assert(offsetof(SmemCtl, full_bar) % 8 == 0 && offsetof(SmemCtl, ring) % 16 == 0, "barrier / ring alignment");
 
 // ------------------------------------------------------------ scoped helpers
 template <bool S>
@@ -261,17 +251,14 @@ __device__ __noinline__ void record_stuck(const FdmoeParams& p, SmemCtl& sc, uin
 }
 
 // Bounded mbarrier wait.  Returns false (after raising the error) on timeout
-// or when another role of this CTA has aborted.  kTight: poll without pause (the TMA and MMA
-// threads, whose reaction time is part of the operand pipeline's round trip); otherwise the
-// waiter sleeps inside try_wait and leaves the issue slots of its SM partition to the others.
-template <bool kTight>
-__device__ __forceinline__ bool wait_bar_t(const FdmoeParams& p, SmemCtl& sc, uint64_t* bar, uint32_t parity,
-                                           uint32_t err_code) {
-  if (ptx::mbar_test_wait(bar, parity)) return ptx::mbar_test_wait_cluster(bar, parity);
+// or when another role of this CTA has aborted.
+__device__ __forceinline__ bool wait_bar(const FdmoeParams& p, SmemCtl& sc, uint64_t* bar,
+                                         uint32_t parity, uint32_t err_code) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = ptx::globaltimer_ns();
   uint32_t spins = 0;
-  while (!(kTight ? ptx::mbar_test_wait(bar, parity) : ptx::mbar_try_wait(bar, parity))) {
-    if ((++spins & (kTight ? 63u : 3u)) == 0u) {
+  while (!ptx::mbar_try_wait(bar, parity)) {
+    if ((++spins & 63u) == 0u) {
       const uint64_t waited = ptx::globaltimer_ns() - t0;
       if (sc.abort) {
         record_stuck(p, sc, bar, parity, err_code | 0x100u, waited);
@@ -284,51 +271,20 @@ __device__ __forceinline__ bool wait_bar_t(const FdmoeParams& p, SmemCtl& sc, ui
       }
     }
   }
-  return ptx::mbar_test_wait_cluster(bar, parity);  // (true) acquires what the partner CTA released with its signal
-}
-__device__ __forceinline__ bool wait_bar(const FdmoeParams& p, SmemCtl& sc, uint64_t* bar, uint32_t parity,
-                                         uint32_t err_code) {
-  return wait_bar_t<true>(p, sc, bar, parity, err_code);
-}
-
-// The same wait for a whole warp of the epilogue group: lane 0 waits (sleeping), the others are
-// parked at the shuffle; every lane then acquires through the (completed) barrier itself.
-__device__ __forceinline__ bool wait_bar_warp(const FdmoeParams& p, SmemCtl& sc, uint64_t* bar, uint32_t parity,
-                                              uint32_t err_code) {
-  int ok = 1;
-  if ((threadIdx.x & 31) == 0) ok = wait_bar_t<false>(p, sc, bar, parity, err_code) ? 1 : 0;
-  ok = __shfl_sync(0xffffffffu, ok, 0);
-  if (ok) (void)ptx::mbar_test_wait_cluster(bar, parity);
-  return ok != 0;
+  return true;
 }
 
 // Same wait without raising an error: one budget's worth of polling.
 __device__ __forceinline__ bool wait_idle(const FdmoeParams& p, SmemCtl& sc, uint64_t* bar, uint32_t parity) {
   const uint64_t t0 = ptx::globaltimer_ns();
   uint32_t spins = 0;
-  while (!ptx::mbar_try_wait_cluster(bar, parity)) {
+  while (!ptx::mbar_try_wait(bar, parity)) {
     if ((++spins & 63u) == 0u) {
       if (sc.abort || ptx::globaltimer_ns() - t0 > p.timeout_ns) return false;
       __nanosleep(200);
     }
   }
   return true;
-}
-
-// ---- signals that go to the leader's copy of a barrier (local for the leader, remote for its partner)
-__device__ __forceinline__ void arrive_on_leader(uint64_t* bar, uint32_t cta) {
-  if (cta == 0u)
-    ptx::mbar_arrive(bar);
-  else
-    ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(bar), 0u));
-}
-// this consumer is done with slot r of its CTA's task ring
-__device__ __forceinline__ void ring_release(SmemCtl& sc, uint32_t cta, uint32_t r) {
-  arrive_on_leader(&sc.ring_empty[cta][r], cta);
-}
-// this warp has drained its part of accumulator `acc`
-__device__ __forceinline__ void acc_release(SmemCtl& sc, uint32_t cta, uint32_t acc) {
-  arrive_on_leader(&sc.tmem_empty[acc], cta);
 }
 
 // ------------------------------------------------------------- global queue
@@ -544,11 +500,11 @@ __device__ __forceinline__ void topk_warp(const float* logits, int E, int K, int
 // GATEFIX task, which recomputes its logits in the reference's order; for every
 // other token both orders select the same experts in the same order.
 template <bool S>
-__device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, uint32_t cta, uint32_t acc,
+__device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, uint64_t* tmem_empty_bar,
                                            int q, int h, int lane, int etid, int ewarp, uint32_t tile) {
   const int E = p.E, K = p.K;
   const int t0 = (int)tile * p.gate_rows;
-  const int nt = max(0, min(p.gate_rows, p.T - t0));  // 0: the pair's second tile lies past the last token
+  const int nt = min(p.gate_rows, p.T - t0);
   const int kk = min(E, 9);
   const int npass = p.gate_rows / 32;
 
@@ -562,7 +518,7 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
     // this warp's TMEM lanes hold no token of the tile: it only has to release the accumulator
     ptx::tcgen05_fence_before();
     __syncwarp();
-    if (lane == 0) acc_release(sc, cta, acc);
+    if (lane == 0) ptx::mbar_arrive(tmem_empty_bar);
   }
   for (int pass = 0; pass < npass; ++pass) {
     if (q == pass) {
@@ -584,7 +540,7 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
       }
       ptx::tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) acc_release(sc, cta, acc);  // this warp is done with the accumulator
+      if (lane == 0) ptx::mbar_arrive(tmem_empty_bar);  // this warp is done with the accumulator
     }
     epi_bar();
     prof_mark(p, sc, etid, 41);
@@ -700,6 +656,34 @@ __device__ __forceinline__ uint32_t pack_rows_per_stage(int H) {
   return min(16u, (uint32_t)kStageBytes / ((uint32_t)H * 2u));
 }
 
+// TMA-warp side of a PACK task (one thread): brings the token rows of the piece into the
+// pipeline stages, up to pack_rows_per_stage() rows per stage.  The source indices of the
+// next stage are fetched while the current one is waited for and issued.
+__device__ __noinline__ bool pack_loads(const FdmoeParams& p, SmemCtl& sc, uint8_t* stage, uint32_t& stage_it,
+                                        uint32_t e, uint32_t first, uint32_t count) {
+  const uint32_t rowb = (uint32_t)p.H * 2u, rps = pack_rows_per_stage(p.H);
+  const int32_t* src_list = p.send_src + (size_t)e * p.send_stride + first;
+  const uint8_t* xb = reinterpret_cast<const uint8_t*>(p.x);
+  int32_t cur[16], nxt[16];
+#pragma unroll
+  for (uint32_t i = 0; i < 16; ++i) cur[i] = (i < rps && i < count) ? __ldcg(src_list + i) : 0;
+  for (uint32_t b0 = 0; b0 < count; b0 += rps, ++stage_it) {
+    const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
+    const uint32_t nrows = min(rps, count - b0);
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) nxt[i] = (i < rps && b0 + rps + i < count) ? __ldcg(src_list + b0 + rps + i) : 0;
+    if (!wait_bar(p, sc, &sc.empty_bar[s], sph ^ 1u, FDMOE_ERR_TIMEOUT_STAGE)) return false;
+    ptx::mbar_expect_tx(&sc.full_bar[s], nrows * rowb);
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i)
+      if (i < nrows)
+        ptx::bulk_load_1d(stage + s * kStageBytes + i * rowb, xb + (size_t)(cur[i] >> 4) * rowb, rowb, &sc.full_bar[s]);
+#pragma unroll
+    for (uint32_t i = 0; i < 16; ++i) cur[i] = nxt[i];
+  }
+  return true;
+}
+
 template <bool S>
 __device__ __noinline__ bool pack_task(const FdmoeParams& p, SmemCtl& sc, uint8_t* stage, uint32_t& stage_it, int etid,
                                        int ewarp, int lane, uint32_t e, uint32_t first, uint32_t count) {
@@ -714,7 +698,7 @@ __device__ __noinline__ bool pack_task(const FdmoeParams& p, SmemCtl& sc, uint8_
     const uint32_t nrows = min(rps, count - b0);
     int32_t d = 0;
     if (ewarp == 0 && (uint32_t)lane < nrows) d = __ldcg(dst_list + b0 + lane);
-    if (!epi_vote_all(wait_bar_warp(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE))) return false;
+    if (!epi_vote_all(wait_bar(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE))) return false;
     if (ewarp == 0) {
       if ((uint32_t)lane < nrows) {
         ptx::bulk_store_1d(packed + (size_t)d * rowb, stage + s * kStageBytes + (uint32_t)lane * rowb, rowb);
@@ -737,27 +721,24 @@ __device__ __noinline__ bool pack_task(const FdmoeParams& p, SmemCtl& sc, uint8_
     const uint32_t total = ld_relaxed<S>(&op.expert_cnt[le]);  // final: every rank has finished gating
     sc.flag = (prev + count == total) ? (int)total : 0;
     if (sc.flag) {
-      const uint32_t ntask = ((total + FDMOE_BLOCK_ROWS - 1u) / FDMOE_BLOCK_ROWS) * (uint32_t)(p.I / FDMOE_TILE_N1);
+      const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
+      const uint32_t ntask = ((total + 127u) / 128u) * nt1;
       fence_acqrel<S>();  // the other senders' rows (observed through the counter) before the tasks
       sc.q_t0 = atom_add<S>(&op.ctl->q_head, ntask);
     }
   }
   epi_bar();
   if (sc.flag) {
-    // Row blocks: as few blocks of at most 256 rows as possible, equal in size up to the 16-row
-    // granule of the tile's N extent.  Column tile major, so that the blocks sharing a weight tile
-    // are neighbours in the queue.
     const uint32_t total = (uint32_t)sc.flag, nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
-    const uint32_t nblk = (total + FDMOE_BLOCK_ROWS - 1u) / FDMOE_BLOCK_ROWS;
-    const uint32_t rpb = ((total + nblk - 1u) / nblk + 15u) & ~15u;
-    const uint32_t ntask = nblk * nt1, t0 = sc.q_t0;
+    const uint32_t full = total / 128u, rem = total % 128u, ntask = ((total + 127u) / 128u) * nt1;
+    const uint32_t t0 = sc.q_t0;
     bool any = false;
     for (uint32_t idx = etid; idx < ntask; idx += kEpiThreads) {
-      const uint32_t n = idx / nblk, j = idx - n * nblk;
+      const uint32_t j = idx / nt1, n = idx - j * nt1;
       FdmoeSlot* sl = &op.slots[(t0 + idx) & (uint32_t)p.queue_mask];
       sl->a = task_word(FDMOE_TASK_FFN1, (uint32_t)le, n);
-      sl->b = j * rpb;
-      sl->c = min(rpb, total - j * rpb);
+      sl->b = j;
+      sl->c = (j < full) ? 128u : rem;
       any = true;
     }
     if (any) {
@@ -799,7 +780,7 @@ __device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uin
     const uint32_t nkb = (uint32_t)(H / FDMOE_TILE_K);
     for (uint32_t kb = 0; kb < nkb; kb += kFixBlocks, ++stage_it) {
       const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
-      if (!epi_vote_all(wait_bar_warp(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE))) return false;
+      if (!epi_vote_all(wait_bar(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE))) return false;
       if (live && e < E) {
         const uint32_t nb = min((uint32_t)kFixBlocks, nkb - kb);
         for (uint32_t i = 0; i < nb; ++i) {
@@ -871,7 +852,7 @@ __device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int e
   // (the task was taken from the queue with an acquire load ordered after every rank's reservations)
   uint32_t ntile = 0, npack = 0, ecnt = 0;
   const int e_send = (etid < p.E) ? (int)(((uint32_t)((p.rank + 1) % p.world) * (uint32_t)p.El + (uint32_t)etid) % (uint32_t)p.E) : 0;
-  if (etid < p.El) ntile = (ld_relaxed<S>(&me.expert_cnt[etid]) + FDMOE_BLOCK_ROWS - 1u) / FDMOE_BLOCK_ROWS;
+  if (etid < p.El) ntile = (ld_relaxed<S>(&me.expert_cnt[etid]) + 127u) / 128u;
   if (etid < p.E) {
     ecnt = __ldcg(&p.send_cnt[e_send]);
     npack = (ecnt + FDMOE_PACK_ROWS - 1) / FDMOE_PACK_ROWS;
@@ -928,95 +909,96 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
-// FFN tiles keep the weights as the M operand, so an accumulator holds output features in
-// its lanes and the rows of the block in its columns: thread (q, lane) of either half of the
-// epilogue group reads feature lane 32q + lane for 32 rows at a time; the two halves take
-// alternate 32-row chunks.
+// Writes one 32-row x 64-byte chunk held as 16 packed words per thread (thread
+// = row) through the warp's staging buffer so that every global store
+// instruction covers 8 rows x 64 contiguous bytes instead of 32 rows x 16.
+// dst[i] / ok[i] describe row (lane >> 2) + 8 i: pointer to the chunk's first
+// byte in global memory and whether the row exists.
+__device__ __forceinline__ void store_chunk_coalesced(uint8_t* st, int lane, const uint32_t (&o)[16],
+                                                      uint8_t* const (&dst)[4], const bool (&ok)[4]) {
+  uint4* mine = reinterpret_cast<uint4*>(st + lane * 80);
+#pragma unroll
+  for (int v = 0; v < 4; ++v) mine[v] = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+  __syncwarp();
+  const int piece = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = (lane >> 2) + 8 * i;
+    const uint4 val = *reinterpret_cast<const uint4*>(st + r * 80 + piece * 16);
+    if (ok[i]) *reinterpret_cast<uint4*>(dst[i] + piece * 16) = val;
+  }
+  __syncwarp();
+}
 
-// FFN1 epilogue.  The CTA's 128 weight rows are 4 x (16 gate rows, 16 up rows of the same
-// features), so lanes l and l + 16 of a warp hold gate and up of feature 16q + (l & 15):
-//   act[row, n*128 + cta*64 + f] = silu(gate[f, row]) * up[f, row]
-// Every warp transposes its 16 features x 32 rows through a staging tile of its own (48-byte
-// pitch), so a row's 16 features leave as one 32-byte piece and nothing is exchanged between warps.
-__device__ __forceinline__ void ffn1_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, uint32_t cta, int q,
-                                              int h, int lane, int ewarp, uint32_t le, uint32_t n, uint32_t r0,
+// FFN1 epilogue: act[row, n*128 + c] = silu(D[row, c]) * D[row, 128 + c].
+__device__ __forceinline__ void ffn1_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, int q, int h,
+                                              int lane, int ewarp, uint32_t e, uint32_t j, uint32_t n,
                                               uint32_t rows) {
-  uint8_t* st = sc.warp_stage[ewarp];
-  const uint32_t nchunk = (rows + 31u) / 32u;
-  uint8_t* actb = reinterpret_cast<uint8_t*>(p.act) +
-                  (((size_t)le * p.cap_rows + r0) * p.I + n * FDMOE_TILE_N1 + cta * 64u + (uint32_t)q * 16u) * 2u;
-  const uint32_t tbase = taddr + ((uint32_t)(q * 32) << 16);
-  const bool lo = lane < 16;
-  const bool skip = (p.debug_flags & 1) != 0;
-  for (uint32_t c = (uint32_t)h; c < nchunk; c += 2) {
-    uint32_t v[32];
-    ptx::tmem_ld_32x32(tbase + c * 32u, v);
+  uint8_t* st = sc.store_stage[ewarp];
+  uint8_t* dst[4];
+  bool ok[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t r = q * 32 + (lane >> 2) + 8 * i;
+    ok[i] = r < rows && !(p.debug_flags & 1);
+    dst[i] = reinterpret_cast<uint8_t*>(reinterpret_cast<bf16*>(p.act) +
+                                        ((size_t)e * p.cap_rows + (size_t)j * 128 + r) * p.I +
+                                        n * FDMOE_TILE_N1 + h * 64);
+  }
+  const uint32_t tbase = taddr + ((uint32_t)(q * 32) << 16) + h * 64;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint32_t g[32], u[32], o[16];
+    ptx::tmem_ld_32x32(tbase + c * 32, g);
+    ptx::tmem_ld_32x32(tbase + 128 + c * 32, u);
     ptx::tmem_ld_wait();
-    uint8_t* dst = st + (lo ? 0 : 16) * 48 + (lane & 15) * 2;
+    prof_mark(p, sc, ewarp * 32 + lane, 10 + c * 3);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      // lanes below 16 keep rows 0..15 and hand their gate of rows 16..31 to the up lane, and vice versa
-      const uint32_t send = lo ? v[16 + i] : v[i];
-      const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 16);
-      const float g = __uint_as_float(lo ? v[i] : recv);
-      const float u = __uint_as_float(lo ? recv : v[16 + i]);
-      *reinterpret_cast<bf16*>(dst + i * 48) = __float2bfloat16_rn(silu_mul(g, u));
-    }
-    __syncwarp();
-    // 32 rows x 32 bytes: lane sends 16 bytes of rows lane / 2 and lane / 2 + 16
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const uint32_t rl = (uint32_t)(lane >> 1) + 16u * (uint32_t)k, row = c * 32u + rl;
-      const uint4 val = *reinterpret_cast<const uint4*>(st + rl * 48 + (lane & 1) * 16);
-      if (row < rows && !skip) *reinterpret_cast<uint4*>(actb + (size_t)row * p.I * 2u + (lane & 1) * 16) = val;
-    }
-    __syncwarp();
+    for (int w = 0; w < 16; ++w)
+      o[w] = pack_bf16(silu_mul(__uint_as_float(g[2 * w]), __uint_as_float(u[2 * w])),
+                       silu_mul(__uint_as_float(g[2 * w + 1]), __uint_as_float(u[2 * w + 1])));
+    uint8_t* d2[4] = {dst[0] + c * 64, dst[1] + c * 64, dst[2] + c * 64, dst[3] + c * 64};
+    prof_mark(p, sc, ewarp * 32 + lane, 11 + c * 3);
+    store_chunk_coalesced(st, lane, o, d2, ok);
+    prof_mark(p, sc, ewarp * 32 + lane, 12 + c * 3);
   }
 }
 
-// FFN2 epilogue: y[token, slot, n*256 + cta*128 + f] = D[f, row] * routing weight of the row,
-// stored on the token's home rank, for the `rows` rows of a sub-block that starts `roff` rows into
-// its block.  sc.tokw holds the block's routing weights, sc.tokdst the
-// element offset of (token, slot, 0) in the home rank's staging area and the home rank.  Every
-// warp transposes its 32 features x 32 rows through a staging tile of its own, so nothing is
-// exchanged between warps.
-__device__ __forceinline__ void ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, uint32_t cta, int q,
-                                              int h, int lane, int ewarp, uint32_t n, uint32_t roff,
+// FFN2 epilogue: y[token, slot, n*256 + c] = D[row, c] * routing weight, stored
+// on the token's home rank.
+__device__ __forceinline__ void ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, int q, int h,
+                                              int lane, int ewarp, uint32_t e, uint32_t j, uint32_t n,
                                               uint32_t rows) {
-  const uint32_t nchunk = (rows + 31u) / 32u;
-  const uint32_t tbase = taddr + ((uint32_t)(q * 32) << 16);
-  const uint32_t col0 = n * FDMOE_TILE_N2 + cta * 128u;  // first of this CTA's 128 features
-  const bool skip = (p.debug_flags & 1) != 0;
-  uint8_t* st = sc.warp_stage[ewarp];
-  for (uint32_t c = (uint32_t)h; c < nchunk; c += 2) {
-    uint32_t v[32];
-    ptx::tmem_ld_32x32(tbase + c * 32u, v);
-    // lane i prepares row 32c + i: where this CTA's 256-byte piece of it goes and its routing weight
-    const uint32_t myrow = c * 32u + (uint32_t)lane;
-    unsigned long long mydst = 0ull;
-    float myw = 0.f;
-    if (myrow < rows && !skip) {
-      const uint2 d = sc.tokdst[roff + myrow];  // {element offset of the row's slot, home rank}
-      mydst = reinterpret_cast<unsigned long long>(reinterpret_cast<bf16*>(p.peers[d.y].ystage) + (size_t)d.x + col0);
-      myw = sc.tokw[roff + myrow];
-    }
+  uint8_t* st = sc.store_stage[ewarp];
+  const uint32_t row = q * 32 + lane;
+  float wgt = 0.f;
+  unsigned long long myptr = 0ull;
+  if (row < rows) {
+    const uint4 mraw = ld_cg_u4(&p.peers[p.rank].meta[(size_t)e * p.cap_rows + (size_t)j * 128 + row]);
+    const int token = (int)mraw.x, home = (int)mraw.y >> 8, slot = (int)mraw.y & 0xff;
+    wgt = __uint_as_float(mraw.z);
+    myptr = reinterpret_cast<unsigned long long>(reinterpret_cast<bf16*>(p.peers[home].ystage) +
+                                                 ((size_t)token * p.K + slot) * p.H + n * FDMOE_TILE_N2 + h * 128);
+  }
+  uint8_t* dst[4];
+  bool ok[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const unsigned long long pp = __shfl_sync(0xffffffffu, myptr, (lane >> 2) + 8 * i);
+    dst[i] = reinterpret_cast<uint8_t*>(pp);
+    ok[i] = pp != 0ull && !(p.debug_flags & 1);
+  }
+  const uint32_t tbase = taddr + ((uint32_t)(q * 32) << 16) + h * 128;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t d[32], o[16];
+    ptx::tmem_ld_32x32(tbase + c * 32, d);
     ptx::tmem_ld_wait();
-    // transpose this warp's 32 features x 32 rows through its own staging tile: a row's 32 features
-    // (64 bytes) then leave as four 16-byte stores, eight rows per store instruction
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float wi = __shfl_sync(0xffffffffu, myw, i);
-      *reinterpret_cast<bf16*>(st + i * 80 + lane * 2) = __float2bfloat16_rn(__uint_as_float(v[i]) * wi);
-    }
-    __syncwarp();
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int r = (lane >> 2) + 8 * k;
-      const uint4 val = *reinterpret_cast<const uint4*>(st + r * 80 + (lane & 3) * 16);
-      const unsigned long long dr = __shfl_sync(0xffffffffu, mydst, r);
-      if (dr != 0ull) *reinterpret_cast<uint4*>(dr + (unsigned long long)(q * 64 + (lane & 3) * 16)) = val;
-    }
-    __syncwarp();
+    for (int w = 0; w < 16; ++w)
+      o[w] = pack_bf16(__uint_as_float(d[2 * w]) * wgt, __uint_as_float(d[2 * w + 1]) * wgt);
+    uint8_t* d2[4] = {dst[0] + c * 64, dst[1] + c * 64, dst[2] + c * 64, dst[3] + c * 64};
+    store_chunk_coalesced(st, lane, o, d2, ok);
   }
 }
 
@@ -1024,161 +1006,6 @@ __device__ __forceinline__ void ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc,
 // shared-memory stage ring with 1-D bulk copies (issued by the TMA warp) in
 // pieces of up to 2048 columns: stage layout [K][piece], 4 KB per slot row.
 constexpr int kCombineCols = 2048;
-
-// Position of a CTA's TMA thread in the two uses of the operand stages: `pit` counts stages
-// filled for pair tiles, `sit` stages filled for single-CTA tasks.  Both walk the same
-// physical stages round robin, so before a stage is filled for one use the last fill for the
-// other use must have been consumed as well.
-struct StageCursor {
-  uint32_t pit, sit;
-  uint64_t w_wait, w_issue;  // (trace) SM cycles spent waiting for a free pair stage / issuing its loads
-};
-// number of x in [0, n) with x % kStages == s
-__device__ __forceinline__ uint32_t stage_uses(uint32_t n, uint32_t s) { return (n + (uint32_t)kStages - 1u - s) / (uint32_t)kStages; }
-
-__device__ __forceinline__ bool stage_for_single(const FdmoeParams& p, SmemCtl& sc, const StageCursor& cur) {
-  const uint32_t s = cur.sit % kStages;
-  if (!wait_bar(p, sc, &sc.empty_bar[s], ((cur.sit / kStages) & 1u) ^ 1u, FDMOE_ERR_TIMEOUT_STAGE)) return false;
-  const uint32_t up = stage_uses(cur.pit, s);
-  return up == 0u || wait_bar(p, sc, &sc.pempty[s], (up - 1u) & 1u, FDMOE_ERR_TIMEOUT_STAGE);
-}
-__device__ __forceinline__ bool stage_for_pair(const FdmoeParams& p, SmemCtl& sc, const StageCursor& cur) {
-  const uint32_t s = cur.pit % kStages;
-  if (!wait_bar(p, sc, &sc.pempty[s], ((cur.pit / kStages) & 1u) ^ 1u, FDMOE_ERR_TIMEOUT_STAGE)) return false;
-  const uint32_t us = stage_uses(cur.sit, s);
-  return us == 0u || wait_bar(p, sc, &sc.empty_bar[s], (us - 1u) & 1u, FDMOE_ERR_TIMEOUT_STAGE);
-}
-
-// TMA-warp side of a PACK task (one thread): brings the token rows of the piece into the
-// pipeline stages, up to pack_rows_per_stage() rows per stage.  The source indices of the
-// next stage are fetched while the current one is waited for and issued.
-__device__ __noinline__ bool pack_loads(const FdmoeParams& p, SmemCtl& sc, uint8_t* stage, StageCursor& cur,
-                                        uint32_t e, uint32_t first, uint32_t count) {
-  const uint32_t rowb = (uint32_t)p.H * 2u, rps = pack_rows_per_stage(p.H);
-  const int32_t* src_list = p.send_src + (size_t)e * p.send_stride + first;
-  const uint8_t* xb = reinterpret_cast<const uint8_t*>(p.x);
-  int32_t cur_src[16], nxt_src[16];
-#pragma unroll
-  for (uint32_t i = 0; i < 16; ++i) cur_src[i] = (i < rps && i < count) ? __ldcg(src_list + i) : 0;
-  for (uint32_t b0 = 0; b0 < count; b0 += rps, ++cur.sit) {
-    const uint32_t s = cur.sit % kStages;
-    const uint32_t nrows = min(rps, count - b0);
-#pragma unroll
-    for (uint32_t i = 0; i < 16; ++i)
-      nxt_src[i] = (i < rps && b0 + rps + i < count) ? __ldcg(src_list + b0 + rps + i) : 0;
-    if (!stage_for_single(p, sc, cur)) return false;
-    ptx::mbar_expect_tx(&sc.full_bar[s], nrows * rowb);
-#pragma unroll
-    for (uint32_t i = 0; i < 16; ++i)
-      if (i < nrows)
-        ptx::bulk_load_1d(stage + s * kStageBytes + i * rowb, xb + (size_t)(cur_src[i] >> 4) * rowb, rowb,
-                          &sc.full_bar[s]);
-#pragma unroll
-    for (uint32_t i = 0; i < 16; ++i) cur_src[i] = nxt_src[i];
-  }
-  return true;
-}
-
-// TMA-warp side of a pair tile (one thread per CTA): per k-block this CTA's 128 rows of the M
-// operand and its half of the N operand, completion counted on the leader's barrier.
-//   GATE  M: this CTA's token tile            N: 64 rows of the gate weights
-//   FFN1  M: 4 x (16 gate + 16 up rows)       N: this CTA's half of each sub-block of the expert's packed rows
-//   FFN2  M: 128 rows of W2                   N: the same rows of the expert's activations
-// (Inlined into the kernel on purpose: there the parameter block is read through the constant bank; behind
-// a call it would be reached through a generic pointer, which costs hundreds of cycles per access.)
-template <bool S>
-__device__ __forceinline__ bool pair_loads(const FdmoeParams& p, SmemCtl& sc, uint8_t* stage, StageCursor& cur,
-                                        uint32_t cta, const FdmoeSlot t) {
-  const uint32_t kind = t.a & 0xffu;
-  // (timing experiment 32: every tile reads the operands of expert 0, column tile 0, so that all loads hit L2)
-  const uint32_t e = (p.debug_flags & 32) ? 0u : (t.a >> 8) & 0xfffu, n = (p.debug_flags & 32) ? 0u : t.a >> 20;
-  const bool f1 = kind == FDMOE_TASK_FFN1, gt = kind == FDMOE_TASK_GATE;
-  const uint32_t nkb = (uint32_t)((f1 || gt) ? p.H : p.I) / FDMOE_TILE_K;
-  // rows of the two sub-blocks' N operands held by this CTA (half of each MMA extent)
-  uint32_t n0 = 0u, n1 = 0u;
-  if (!gt) fdmoe_split_rows(t.c, &n0, &n1);
-  const uint32_t nh0 = ((n0 + 15u) & ~15u) >> 1, nh1 = ((n1 + 15u) & ~15u) >> 1;
-  const uint32_t row0 = e * (uint32_t)p.cap_rows + ((p.debug_flags & 32) ? 0u : t.b);
-  const int32_t brow0 = (int32_t)(row0 + cta * nh0), brow1 = (int32_t)(row0 + n0 + cta * nh1);
-  // GATE boxes are clamped to the tensor extents, and a box that lies wholly outside is not requested at all
-  const bool gate_b = cta * 64u < (uint32_t)p.E;  // this CTA's 64 gate-weight rows exist (at least partly)
-  const bool gate_a = (2u * t.b + cta) * (uint32_t)p.gate_rows < (uint32_t)p.T;  // this CTA's token tile exists
-  // Bytes both CTAs bring into a stage.  The leader alone arrives on its barrier, announcing them;
-  // the partner's copies only add their completed bytes.
-  uint32_t pair_bytes;
-  if (gt) {
-    const uint32_t tiles = ((2u * t.b) * (uint32_t)p.gate_rows < (uint32_t)p.T ? 1u : 0u) +
-                           ((2u * t.b + 1u) * (uint32_t)p.gate_rows < (uint32_t)p.T ? 1u : 0u);
-    const uint32_t wboxes = 64 < p.E ? 2u : 1u;
-    pair_bytes = (tiles * (uint32_t)min(p.gate_rows, p.T) + wboxes * (uint32_t)min(64, p.E)) * FDMOE_TILE_K * 2u;
-  } else {
-    pair_bytes = 2u * (128u + nh0 + nh1) * FDMOE_TILE_K * 2u;
-  }
-  const FdmoeTensorMap* const bmaps = f1 ? p.tm_packed_rows : p.tm_act_rows;  // entry i: box of 8 (i + 1) rows
-  const FdmoeTensorMap* const bmap0 = gt ? nullptr : bmaps + (nh0 / 8u - 1u);
-  const FdmoeTensorMap* const bmap1 = nh1 ? bmaps + (nh1 / 8u - 1u) : nullptr;
-  const uint32_t dbg = (uint32_t)p.debug_flags;
-  const FdmoeTensorMap* const map_w13 = &p.tm_w13;
-  const FdmoeTensorMap* const map_w2 = &p.tm_w2;
-  ptx::fence_proxy_async();  // rows / activations were written with generic stores or bulk copies
-  for (uint32_t kb = 0; kb < nkb; ++kb, ++cur.pit) {
-    const uint32_t s = cur.pit % kStages;
-    const long long tw = clock64();
-    if (!stage_for_pair(p, sc, cur)) return false;
-    const long long tq = clock64();
-    cur.w_wait += (uint64_t)(tq - tw);
-    uint8_t* sa = stage + s * kStageBytes;
-    uint8_t* sb = sa + kStageA;
-    const uint32_t full0 = ptx::map_to_cta(ptx::smem_u32(&sc.pfull[s]), 0u);
-    if ((dbg & 8u) && !gt) {  // timing experiment: tiles computed from stale operands
-      if (cta == 0u) ptx::mbar_arrive(&sc.pfull[s]);
-      continue;
-    }
-    if (cta == 0u) ptx::mbar_expect_tx(&sc.pfull[s], pair_bytes);
-    const int32_t kx = (int32_t)(kb * FDMOE_TILE_K);
-    if (gt) {
-      if (gate_a) ptx::tma_load_2d_pair(sa, &p.tm_x, full0, kx, (int32_t)((2u * t.b + cta) * (uint32_t)p.gate_rows));
-      if (gate_b) ptx::tma_load_2d_pair(sb, &p.tm_gate, full0, kx, (int32_t)(cta * 64u));
-      continue;
-    }
-    if (f1) {
-      // four groups of (16 gate rows, 16 up rows) in one box
-      const int32_t grp = (int32_t)((n * FDMOE_TILE_N1 + cta * 64u) / 16u);
-      ptx::tma_load_5d_pair(sa, map_w13, full0, kx, 0, 0, grp, (int32_t)e);
-      // The weights come from HBM: ask L2 for them kPrefetch k-blocks ahead, so that the
-      // shared-memory stages only have to cover the L2 latency.
-      if (kb + kPrefetch < nkb && (dbg & 16u)) ptx::tma_prefetch_l2_5d(map_w13, kx + kPrefetch * FDMOE_TILE_K, 0, 0, grp, (int32_t)e);
-    } else {
-      const int32_t wrow = (int32_t)(e * (uint32_t)p.H + n * FDMOE_TILE_N2 + cta * 128u);
-      ptx::tma_load_2d_pair(sa, map_w2, full0, kx, wrow);
-      if (kb + kPrefetch < nkb && (dbg & 16u)) ptx::tma_prefetch_l2_2d(map_w2, kx + kPrefetch * FDMOE_TILE_K, wrow);
-    }
-    // this CTA's half of each sub-block's rows in one box (descriptor chosen by its height)
-    ptx::tma_load_2d_pair(sb, bmap0, full0, kx, brow0);
-    if (nh1) ptx::tma_load_2d_pair(sb + kStageB, bmap1, full0, kx, brow1);
-    cur.w_issue += (uint64_t)(clock64() - tq);
-  }
-  return true;
-}
-
-// Leader's scheduler: writes task `t` into slot r of CTA c's ring and signals it.
-__device__ __forceinline__ void ring_deliver(SmemCtl& sc, uint32_t c, uint32_t r, const FdmoeSlot& t) {
-  if (c == 0u) {
-    sc.ring[r] = t;
-    ptx::mbar_arrive(&sc.ring_full[r]);
-  } else {
-    const uint32_t dst = ptx::map_to_cta(ptx::smem_u32(&sc.ring[r]), 1u);
-    ptx::st_cluster_u32(dst + 0, t.seq);
-    ptx::st_cluster_u32(dst + 4, t.a);
-    ptx::st_cluster_u32(dst + 8, t.b);
-    ptx::st_cluster_u32(dst + 12, t.c);
-    ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&sc.ring_full[r]), 1u));
-  }
-}
-
-__device__ __forceinline__ bool is_pair_task(uint32_t kind) {
-  return kind == FDMOE_TASK_GATE || kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2;
-}
 
 template <bool S>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -1190,48 +1017,53 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
   SmemCtl& sc = *reinterpret_cast<SmemCtl*>(stage + kStages * kStageBytes);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t cta = ptx::cluster_ctarank();  // 0: leader of the pair, 1: its partner
   const FdmoePeer& me = p.peers[p.rank];
   FdmoeCtl* ctl = me.ctl;
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(&sc.pfull[s], 1);  // the leader's arrival, which announces the bytes of both CTAs
-      ptx::mbar_init(&sc.pempty[s], 1);
       ptx::mbar_init(&sc.full_bar[s], 1);
       ptx::mbar_init(&sc.empty_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(&sc.tmem_full[a], 1);
-      ptx::mbar_init(&sc.tmem_empty[a], 2 * (kEpiThreads / 32));  // the epilogue warps of both CTAs
+      ptx::mbar_init(&sc.tmem_empty[a], kEpiThreads / 32);
     }
     for (int r = 0; r < kRing; ++r) {
       ptx::mbar_init(&sc.ring_full[r], 1);
-      ptx::mbar_init(&sc.ring_empty[0][r], 2 + kEpiThreads / 32);
-      ptx::mbar_init(&sc.ring_empty[1][r], 2 + kEpiThreads / 32);
+      ptx::mbar_init(&sc.ring_empty[r], 2 + kEpiThreads / 32);
     }
     for (int d = 0; d < kDone; ++d) {
       ptx::mbar_init(&sc.done_full[d], 1);
       ptx::mbar_init(&sc.done_empty[d], 1);
     }
     sc.abort = 0;
+    sc.skip_done = 0;
     sc.flag = 0;
     sc.prof_n = 0;
     ptx::fence_mbar_init();
-    if (blockIdx.x == 0) st_relaxed<S>(&ctl->tokens_launch, (uint32_t)p.T);
+    st_relaxed<S>(&ctl->tokens_launch, (uint32_t)p.T);
+  }
+  {
+    static_assert(sizeof(FdmoeParams) % 16 == 0, "parameter block is copied in 16-byte pieces");
+    const uint4* src = reinterpret_cast<const uint4*>(&p);
+    uint4* dst = reinterpret_cast<uint4*>(&sc.params);
+    for (int i = tid; i < (int)(sizeof(FdmoeParams) / 16); i += kThreads) dst[i] = src[i];
   }
   if (warp == kWarpTmem) {
-    ptx::tmem_alloc2(&sc.tmem_base, kTmemCols);
-    ptx::tmem_relinquish2();
+    ptx::tmem_alloc(&sc.tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
   }
   if (warp == kWarpTma && lane == 0) {
+    ptx::prefetch_tmap(&p.tm_packed);
     ptx::prefetch_tmap(&p.tm_w13);
+    ptx::prefetch_tmap(&p.tm_act);
     ptx::prefetch_tmap(&p.tm_w2);
     ptx::prefetch_tmap(&p.tm_x);
     ptx::prefetch_tmap(&p.tm_gate);
   }
   ptx::tcgen05_fence_before();
-  ptx::cluster_sync();  // both CTAs' barriers exist before either signals the other's
+  __syncthreads();
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = sc.tmem_base;
 
@@ -1256,21 +1088,18 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
     __syncthreads();
   }
 
-  // ---- seed the queue: the leader of every pair publishes its share of the GATE tasks (two
-  // token tiles each: task b covers tiles 2b and 2b + 1), so that all tiles are available at
-  // once.  Nothing to gate: the rank's "gate phase" is finished at once (it may still serve
-  // its peers).
-  if (p.mode != 2 && !sc.abort && tid == 0 && cta == 0u) {
-    const uint32_t n_tiles =
-        (p.T > 0 && p.gate_rows > 0) ? (uint32_t)((p.T + p.gate_rows - 1) / p.gate_rows) : 0u;
-    const uint32_t n_tasks = (n_tiles + 1u) / 2u, pair = blockIdx.x / 2u, n_pairs = gridDim.x / 2u;
+  // ---- seed the queue: every CTA publishes its share of the GATE tasks (tile b, b + grid, ...),
+  // so that all tiles are available at once.  Nothing to gate: the rank's "gate phase" is
+  // finished at once (it may still serve its peers).
+  if (p.mode != 2 && !sc.abort && tid == 0) {
+    const uint32_t n_tiles = (p.T > 0 && p.gate_rows > 0) ? (uint32_t)((p.T + p.gate_rows - 1) / p.gate_rows) : 0u;
     if (n_tiles == 0) {
       if (blockIdx.x == 0) gating_finished<S>(p);
-    } else if (pair < n_tasks) {
-      const uint32_t mine = (n_tasks - pair + n_pairs - 1) / n_pairs;
-      queue_push<false>(p, me, mine, [=](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
+    } else if (blockIdx.x < n_tiles) {
+      const uint32_t mine = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+      queue_push<false>(p, me, mine, [](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
         a = FDMOE_TASK_GATE;
-        b = pair + i * n_pairs;
+        b = blockIdx.x + i * gridDim.x;
         c = 0;
       });
     }
@@ -1281,114 +1110,105 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
   const uint32_t nkb1 = (uint32_t)(p.H / FDMOE_TILE_K), nkb2 = (uint32_t)(p.I / FDMOE_TILE_K);
 
   if (warp == kWarpSched) {
-    if (lane == 0 && cta == 0u) {
-      // One scheduler per pair.  Pair tiles go into both CTAs' rings (in the same order), other
-      // tasks to one CTA.  Tile tasks, COMBINE and PACK are queued behind one another (their
-      // loads run ahead of the consumers); behind a task of another kind a claimed ticket would
-      // just sit in the ring while other workers idle, so such a CTA gets nothing more until it
-      // has finished.
-      uint32_t it[2] = {0u, 0u};
-      uint32_t held[2] = {0u, 0u}, held_r[2] = {0u, 0u}, held_ph[2] = {0u, 0u};
-      uint32_t pref = 0u;
-      bool alive = true;
-      while (alive) {
-        // wait until one of the two CTAs can take a task
-        int c = -1;
-        const uint64_t t0w = ptx::globaltimer_ns();
-        for (uint32_t spins = 0; c < 0; ++spins) {
-          for (uint32_t k = 0; k < 2u && c < 0; ++k) {
-            const uint32_t cc = (pref + k) & 1u;
-            if (held[cc]) {
-              if (!ptx::mbar_test_wait(&sc.ring_empty[cc][held_r[cc]], held_ph[cc])) continue;
-              held[cc] = 0u;
-            }
-            if (ptx::mbar_test_wait(&sc.ring_empty[cc][it[cc] % kRing], ((it[cc] / kRing) & 1u) ^ 1u)) c = (int)cc;
-          }
-          if (c < 0) __nanosleep(64);
-          if (c < 0 && (spins & 63u) == 63u) {
-            if (sc.abort) break;
-            if (ptx::globaltimer_ns() - t0w > p.timeout_ns) {
-              raise_error(p, sc, FDMOE_ERR_TIMEOUT_RING, (blockIdx.x << 8));
-              break;
-            }
-          }
+    if (lane == 0) {
+      for (uint32_t it = 0;; ++it) {
+        const uint32_t r = it % kRing, ph = (it / kRing) & 1u;
+        if (!wait_bar(p, sc, &sc.ring_empty[r], ph ^ 1u, FDMOE_ERR_TIMEOUT_RING)) {
+          // The ring may be wedged: hand out EXIT through every slot that is free.
+          break;
         }
-        FdmoeSlot t;
-        if (c < 0) {
-          // the pair is wedged or aborted: tell both CTAs to leave through whatever slot is next
-          t.seq = 0;
-          t.a = FDMOE_TASK_EXIT;
-          t.b = t.c = 0;
-        } else {
-          t = queue_pop<S>(p, sc);
-        }
+        const FdmoeSlot t = queue_pop<S>(p, sc);
+        sc.ring[r] = t;
+        ptx::mbar_arrive(&sc.ring_full[r]);
         const uint32_t kind = t.a & 0xffu;
-        if (kind == FDMOE_TASK_EXIT || is_pair_task(kind)) {
-          for (uint32_t cc = 0; cc < 2u; ++cc) {
-            const uint32_t r = it[cc] % kRing, ph = (it[cc] / kRing) & 1u;
-            if (kind != FDMOE_TASK_EXIT || c >= 0) {
-              if (!wait_bar(p, sc, &sc.ring_empty[cc][r], ph ^ 1u, FDMOE_ERR_TIMEOUT_RING)) {
-                alive = false;  // (falls through: the slot is overwritten with the task anyway; the CTA is aborting)
-              }
-            }
-            ring_deliver(sc, cc, r, t);
-            if (kind == FDMOE_TASK_GATE) {
-              held[cc] = 1u;
-              held_r[cc] = r;
-              held_ph[cc] = ph;
-            }
-            ++it[cc];
-          }
-          if (kind == FDMOE_TASK_EXIT) alive = false;
-        } else {
-          const uint32_t cc = (uint32_t)c, r = it[cc] % kRing, ph = (it[cc] / kRing) & 1u;
-          ring_deliver(sc, cc, r, t);
-          if (kind != FDMOE_TASK_COMBINE && kind != FDMOE_TASK_PACK) {
-            held[cc] = 1u;
-            held_r[cc] = r;
-            held_ph[cc] = ph;
-          }
-          ++it[cc];
-          pref = cc ^ 1u;
+        if (kind == FDMOE_TASK_EXIT) break;
+        if (kind != FDMOE_TASK_FFN1 && kind != FDMOE_TASK_FFN2 && kind != FDMOE_TASK_COMBINE && kind != FDMOE_TASK_PACK) {
+          // Only tile tasks (and COMBINE / PACK, whose rows travel as bulk copies) profit from being queued behind one another (their loads and
+          // MMAs run ahead of the epilogue).  Behind a long task of another kind a claimed
+          // ticket would just sit here while other workers idle: wait until it is done.
+          if (!wait_bar(p, sc, &sc.ring_empty[r], ph, FDMOE_ERR_TIMEOUT_RING)) break;
         }
       }
     }
     __syncwarp();
   } else if (warp == kWarpTma) {
     if (lane == 0) {
-      StageCursor cur = {0u, 0u, 0ull, 0ull};
+      uint32_t stage_it = 0;
       for (uint32_t it = 0;; ++it) {
         const uint32_t r = it % kRing, ph = (it / kRing) & 1u;
         if (!wait_bar(p, sc, &sc.ring_full[r], ph, FDMOE_ERR_TIMEOUT_RING)) break;
         const FdmoeSlot t = sc.ring[r];
         const uint32_t kind = t.a & 0xffu;
         if (kind == FDMOE_TASK_EXIT) break;
-        bool ok = true;
-        if (is_pair_task(kind)) {
-          ok = pair_loads<S>(p, sc, stage, cur, cta, t);
+        if (kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2 || kind == FDMOE_TASK_GATE) {
+          const uint32_t e = (t.a >> 8) & 0xfffu, n = t.a >> 20, j = t.b;
+          const bool f1 = kind == FDMOE_TASK_FFN1, gt = kind == FDMOE_TASK_GATE;
+          const uint32_t nkb = (f1 || gt) ? nkb1 : nkb2;
+          const int32_t arow = gt ? (int32_t)(j * (uint32_t)p.gate_rows) : (int32_t)(e * (uint32_t)p.cap_rows + j * 128u);
+          // bytes one GATE stage receives: both boxes are clamped to the tensor extents
+          const uint32_t gate_bytes = (uint32_t)(min(p.gate_rows, p.T) + min(128, p.E)) * FDMOE_TILE_K * 2u;
+          ptx::fence_proxy_async();  // rows / activations were written with generic stores
+          bool ok = true;
+          for (uint32_t kb = 0; kb < nkb && ok; ++kb, ++stage_it) {
+            const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
+            ok = wait_bar(p, sc, &sc.empty_bar[s], sph ^ 1u, FDMOE_ERR_TIMEOUT_STAGE);
+            if (!ok) break;
+            uint8_t* sa = stage + s * kStageBytes;
+            uint8_t* sb = sa + kStageA;
+            if ((p.debug_flags & 8) && !gt) {  // timing experiment: tiles computed from stale operands
+              ptx::mbar_arrive(&sc.full_bar[s]);
+              continue;
+            }
+            ptx::mbar_expect_tx(&sc.full_bar[s], gt ? gate_bytes : (uint32_t)kStageBytes);
+            const int32_t kx = (int32_t)(kb * FDMOE_TILE_K);
+            if (gt) {
+              ptx::tma_load_2d(sa, &p.tm_x, &sc.full_bar[s], kx, arow);
+              ptx::tma_load_2d(sb, &p.tm_gate, &sc.full_bar[s], kx, 0);
+            } else if (f1) {
+              ptx::tma_load_2d(sa, &p.tm_packed, &sc.full_bar[s], kx, arow);
+              const int32_t brow = (int32_t)(e * 2u * (uint32_t)p.I + n * FDMOE_TILE_N1);
+              ptx::tma_load_2d(sb, &p.tm_w13, &sc.full_bar[s], kx, brow);
+              ptx::tma_load_2d(sb + kStageA, &p.tm_w13, &sc.full_bar[s], kx, brow + p.I);
+              // The weights come from HBM: ask L2 for them kPrefetch k-blocks ahead, so that the
+              // shared-memory stages only have to cover the L2 latency.
+              if (kb + kPrefetch < nkb) {
+                ptx::tma_prefetch_l2_2d(&p.tm_w13, kx + kPrefetch * FDMOE_TILE_K, brow);
+                ptx::tma_prefetch_l2_2d(&p.tm_w13, kx + kPrefetch * FDMOE_TILE_K, brow + p.I);
+              }
+            } else {
+              ptx::tma_load_2d(sa, &p.tm_act, &sc.full_bar[s], kx, arow);
+              const int32_t brow = (int32_t)(e * (uint32_t)p.H + n * FDMOE_TILE_N2);
+              ptx::tma_load_2d(sb, &p.tm_w2, &sc.full_bar[s], kx, brow);
+              if (kb + kPrefetch < nkb) ptx::tma_prefetch_l2_2d(&p.tm_w2, kx + kPrefetch * FDMOE_TILE_K, brow);
+            }
+          }
+          if (!ok) break;
         } else if (kind == FDMOE_TASK_GATEFIX) {
-          const uint32_t erows = (uint32_t)min(128, p.E);
-          for (uint32_t kb = 0; kb < nkb1 && ok; kb += kFixBlocks, ++cur.sit) {
-            const uint32_t s = cur.sit % kStages;
-            ok = stage_for_single(p, sc, cur);
+          bool ok = true;
+          for (uint32_t kb = 0; kb < nkb1; kb += kFixBlocks, ++stage_it) {
+            const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
+            ok = wait_bar(p, sc, &sc.empty_bar[s], sph ^ 1u, FDMOE_ERR_TIMEOUT_STAGE);
             if (!ok) break;
             const uint32_t nb = min((uint32_t)kFixBlocks, nkb1 - kb);
-            ptx::mbar_expect_tx(&sc.full_bar[s], nb * erows * FDMOE_TILE_K * 2u);
+            const uint32_t blk_bytes = (uint32_t)min(128, p.E) * FDMOE_TILE_K * 2u;
+            ptx::mbar_expect_tx(&sc.full_bar[s], nb * blk_bytes);
             for (uint32_t i = 0; i < nb; ++i)
-              for (uint32_t r0 = 0; r0 < erows; r0 += 64u)  // the gate weights come in boxes of 64 rows
-                ptx::tma_load_2d(stage + s * kStageBytes + i * kStageA + r0 * 128u, &p.tm_gate, &sc.full_bar[s],
-                                 (int32_t)((kb + i) * FDMOE_TILE_K), (int32_t)r0);
+              ptx::tma_load_2d(stage + s * kStageBytes + i * kStageA, &p.tm_gate, &sc.full_bar[s],
+                               (int32_t)((kb + i) * FDMOE_TILE_K), 0);
           }
+          if (!ok) break;
         } else if (kind == FDMOE_TASK_PACK) {
-          ok = pack_loads(p, sc, stage, cur, (t.a >> 8) & 0xfffu, t.b, t.c);
+          const bool ok = pack_loads(sc.params, sc, stage, stage_it, (t.a >> 8) & 0xfffu, t.b, t.c);
+          if (!ok) break;
         } else if (kind == FDMOE_TASK_COMBINE) {
           const int t_begin = (int)t.b, t_end = t_begin + (int)t.c;
           const bf16* ys = reinterpret_cast<const bf16*>(me.ystage);
           ptx::fence_proxy_async();  // the rows were written with generic stores
+          bool ok = true;
           for (int tk = t_begin; tk < t_end && ok; ++tk) {
-            for (int c0 = 0; c0 < p.H; c0 += kCombineCols, ++cur.sit) {
-              const uint32_t s = cur.sit % kStages;
-              ok = stage_for_single(p, sc, cur);
+            for (int c0 = 0; c0 < p.H; c0 += kCombineCols, ++stage_it) {
+              const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
+              ok = wait_bar(p, sc, &sc.empty_bar[s], sph ^ 1u, FDMOE_ERR_TIMEOUT_STAGE);
               if (!ok) break;
               const uint32_t wbytes = (uint32_t)min(kCombineCols, p.H - c0) * 2u;
               uint8_t* sa = stage + s * kStageBytes;
@@ -1398,101 +1218,93 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
                                   &sc.full_bar[s]);
             }
           }
+          if (!ok) break;
         }
-        if (!ok) break;
-        ring_release(sc, cta, r);
-      }
-      if (p.prof) {
-        uint32_t* ev = p.prof + ((size_t)blockIdx.x * FDMOE_PROF_EVENTS + (FDMOE_PROF_EVENTS - 2)) * 4;
-        ev[0] = cur.pit;
-        ev[1] = (uint32_t)(cur.w_wait >> 10);
-        ev[2] = (uint32_t)(cur.w_issue >> 10);
-        ev[3] = cta;
+        ptx::mbar_arrive(&sc.ring_empty[r]);
       }
     }
     __syncwarp();
   } else if (warp == kWarpMma) {
     if (lane == 0) {
-      // Only the leader issues MMAs; its partner's thread just follows the ring.
-      uint32_t pit = 0, tile_it = 0;
-      uint64_t w_full = 0, w_issue = 0, w_acc = 0;  // (trace) time spent waiting for operands / issuing / waiting for an accumulator
+      constexpr uint32_t idesc256 = ptx::make_idesc_bf16(128, 256);
+      constexpr uint32_t idesc128 = ptx::make_idesc_bf16(128, 128);
+      uint32_t stage_it = 0, tile_it = 0, skips = 0;
       for (uint32_t it = 0;; ++it) {
         const uint32_t r = it % kRing, ph = (it / kRing) & 1u;
         if (!wait_bar(p, sc, &sc.ring_full[r], ph, FDMOE_ERR_TIMEOUT_RING)) break;
         const FdmoeSlot t = sc.ring[r];
         const uint32_t kind = t.a & 0xffu;
         if (kind == FDMOE_TASK_EXIT) break;
-        if (is_pair_task(kind) && cta == 0u) {
+        if (kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2 || kind == FDMOE_TASK_GATE) {
           const uint32_t nkb = (kind == FDMOE_TASK_FFN2) ? nkb2 : nkb1;
-          // one accumulator per sub-block (GATE: one, 128 columns)
-          uint32_t n0 = 128u, n1 = 0u;
-          if (kind != FDMOE_TASK_GATE) fdmoe_split_rows(t.c, &n0, &n1);
-          const uint32_t idesc0 = ptx::make_idesc_bf16(256, (n0 + 15u) & ~15u);
-          const uint32_t idesc1 = ptx::make_idesc_bf16(256, (n1 + 15u) & ~15u);
-          const uint32_t acc0 = tile_it & 1u, aph0 = (tile_it >> 1) & 1u;
-          const uint32_t acc1 = (tile_it + 1u) & 1u, aph1 = ((tile_it + 1u) >> 1) & 1u;
-          tile_it += n1 ? 2u : 1u;
-          const long long ta = clock64();
-          if (!wait_bar(p, sc, &sc.tmem_empty[acc0], aph0 ^ 1u, FDMOE_ERR_TIMEOUT_TMEM)) break;
-          if (n1 && !wait_bar(p, sc, &sc.tmem_empty[acc1], aph1 ^ 1u, FDMOE_ERR_TIMEOUT_TMEM)) break;
-          w_acc += (uint64_t)(clock64() - ta);
+          const uint32_t idesc = (kind == FDMOE_TASK_GATE) ? idesc128 : idesc256;
+          const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
+          ++tile_it;
+          if (!wait_bar(p, sc, &sc.tmem_empty[acc], aph ^ 1u, FDMOE_ERR_TIMEOUT_TMEM)) break;
           ptx::tcgen05_fence_after();
-          const uint32_t d0 = tmem_base + acc0 * kAccCols, d1 = tmem_base + acc1 * kAccCols;
+          const uint32_t d_tmem = tmem_base + acc * kAccCols;
           bool ok = true;
-          for (uint32_t kb = 0; kb < nkb; ++kb, ++pit) {
-            const uint32_t s = pit % kStages, sph = (pit / kStages) & 1u;
-            const long long tf = clock64();
-            ok = wait_bar(p, sc, &sc.pfull[s], sph, FDMOE_ERR_TIMEOUT_STAGE);
+          for (uint32_t kb = 0; kb < nkb; ++kb, ++stage_it) {
+            const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
+            ok = wait_bar(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE);
             if (!ok) break;
-            const long long ti = clock64();
-            w_full += (uint64_t)(ti - tf);
             ptx::tcgen05_fence_after();
             const uint32_t sa = ptx::smem_u32(stage + s * kStageBytes);
             const uint64_t da = ptx::make_smem_desc_sw128(sa);
-            const uint64_t db0 = ptx::make_smem_desc_sw128(sa + kStageA);
-            const uint64_t db1 = ptx::make_smem_desc_sw128(sa + kStageA + kStageB);
+            const uint64_t db = ptx::make_smem_desc_sw128(sa + kStageA);
 #pragma unroll
             for (uint32_t k4 = 0; k4 < FDMOE_TILE_K / 16; ++k4) {
               // +32 bytes per 16-element k step inside the 128-byte swizzle row
-              ptx::umma_bf16_pair(d0, da + k4 * 2u, db0 + k4 * 2u, idesc0, (kb | k4) != 0u);
-              if (n1) ptx::umma_bf16_pair(d1, da + k4 * 2u, db1 + k4 * 2u, idesc1, (kb | k4) != 0u);
+              ptx::umma_bf16(d_tmem, da + k4 * 2u, db + k4 * 2u, idesc, (kb | k4) != 0u);
             }
-            // frees the stage in both CTAs when the MMAs have read it
-            const uint32_t eb = ptx::smem_u32(&sc.pempty[s]);
-            ptx::umma_commit_pair(eb);
-            ptx::umma_commit_pair(ptx::map_to_cta(eb, 1u));
-            w_issue += (uint64_t)(clock64() - ti);
+            ptx::umma_commit(&sc.empty_bar[s]);  // frees the stage when the MMAs have read it
           }
           if (!ok) break;
-          const uint32_t fb0 = ptx::smem_u32(&sc.tmem_full[acc0]);
-          ptx::umma_commit_pair(fb0);
-          ptx::umma_commit_pair(ptx::map_to_cta(fb0, 1u));
-          if (n1) {
-            const uint32_t fb1 = ptx::smem_u32(&sc.tmem_full[acc1]);
-            ptx::umma_commit_pair(fb1);
-            ptx::umma_commit_pair(ptx::map_to_cta(fb1, 1u));
+          ptx::umma_commit(&sc.tmem_full[acc]);
+        } else if (kind == FDMOE_TASK_GATEFIX || kind == FDMOE_TASK_COMBINE || kind == FDMOE_TASK_PACK) {
+          // The stages of these tasks are consumed by the epilogue warps.  This warp must not
+          // run ahead of them: a stage barrier only tells phases apart by parity, so a waiter
+          // more than one phase ahead would take an old completion for its own.  Wait until
+          // the epilogue has finished the task, then step over its stages.
+          ++skips;
+          const uint64_t t0w = ptx::globaltimer_ns();
+          uint32_t spins = 0;
+          bool ok = true;
+          while (sc.skip_done < skips) {
+            if ((++spins & 63u) == 0u) {
+              if (sc.abort) { ok = false; break; }
+              if (ptx::globaltimer_ns() - t0w > 4ull * p.timeout_ns) {
+                raise_error(p, sc, FDMOE_ERR_TIMEOUT_STAGE, (blockIdx.x << 8) | 2u);
+                ok = false;
+                break;
+              }
+              __nanosleep(100);
+            }
+          }
+          if (!ok) break;
+          if (kind == FDMOE_TASK_GATEFIX) {
+            stage_it += (nkb1 + kFixBlocks - 1) / kFixBlocks;
+          } else if (kind == FDMOE_TASK_PACK) {
+            const uint32_t rps = pack_rows_per_stage(p.H);
+            stage_it += (t.c + rps - 1u) / rps;
+          } else {
+            const int t_begin = (int)t.b, t_end = t_begin + (int)t.c;
+            stage_it += (uint32_t)((t_end - t_begin) * ((p.H + kCombineCols - 1) / kCombineCols));
           }
         }
-        ring_release(sc, cta, r);
-      }
-      if (p.prof) {
-        uint32_t* ev = p.prof + ((size_t)blockIdx.x * FDMOE_PROF_EVENTS + (FDMOE_PROF_EVENTS - 1)) * 4;
-        ev[0] = pit;
-        ev[1] = (uint32_t)(w_full >> 10);  // units of 1024 SM cycles
-        ev[2] = (uint32_t)(w_issue >> 10);
-        ev[3] = (uint32_t)(w_acc >> 10);
+        ptx::mbar_arrive(&sc.ring_empty[r]);
       }
     }
     __syncwarp();
   } else if (warp >= kWarpEpi0) {
     const int etid = tid - kWarpEpi0 * 32, ewarp = warp - kWarpEpi0;
     const int q = warp & 3, h = ewarp >> 2;
-    uint32_t tile_it = 0, done_it = 0, stage_it = 0;  // stage_it: stages of single-CTA tasks consumed here
+    uint32_t tile_it = 0, done_it = 0, stage_it = 0;
     for (uint32_t it = 0;; ++it) {
       const uint32_t r = it % kRing, ph = (it / kRing) & 1u;
       // the group leaves together: a lone warp breaking out would strand the
       // others at the next group barrier
-      if (!epi_vote_all(wait_bar_warp(p, sc, &sc.ring_full[r], ph, FDMOE_ERR_TIMEOUT_RING))) break;
+      if (!epi_vote_all(wait_bar(p, sc, &sc.ring_full[r], ph, FDMOE_ERR_TIMEOUT_RING))) break;
       const FdmoeSlot t = sc.ring[r];
       const uint32_t kind = t.a & 0xffu;
       if (kind == FDMOE_TASK_EXIT) break;
@@ -1502,48 +1314,38 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       if (kind == FDMOE_TASK_GATE) {
         const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
         ++tile_it;
-        if (!epi_vote_all(wait_bar_warp(p, sc, &sc.tmem_full[acc], aph, FDMOE_ERR_TIMEOUT_TMEM))) break;
+        stage_it += nkb1;
+        if (!epi_vote_all(wait_bar(p, sc, &sc.tmem_full[acc], aph, FDMOE_ERR_TIMEOUT_TMEM))) break;
         if (p.prof && etid == 0) pt1 = prof_now();
         ptx::tcgen05_fence_after();
-        gate_epilogue<S>(p, sc, tmem_base + acc * kAccCols, cta, acc, q, h, lane, etid, ewarp, 2u * j + cta);
+        gate_epilogue<S>(sc.params, sc, tmem_base + acc * kAccCols, &sc.tmem_empty[acc], q, h, lane, etid, ewarp, j);
       } else if (kind == FDMOE_TASK_PACK) {
-        if (!pack_task<S>(p, sc, stage, stage_it, etid, ewarp, lane, e, j, rows)) break;
+        if (!pack_task<S>(sc.params, sc, stage, stage_it, etid, ewarp, lane, e, j, rows)) break;
+        if (etid == 0) {
+          __threadfence_block();
+          sc.skip_done = sc.skip_done + 1u;
+        }
       } else if (kind == FDMOE_TASK_GATEFIX) {
-        if (!gatefix_task<S>(p, sc, stage, stage_it, etid, ewarp, lane, j, rows)) break;
+        if (!gatefix_task<S>(sc.params, sc, stage, stage_it, etid, ewarp, lane, j, rows)) break;
+        if (etid == 0) {
+          __threadfence_block();
+          sc.skip_done = sc.skip_done + 1u;
+        }
       } else if (kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2) {
-        if (kind == FDMOE_TASK_FFN2) {
-          // sideband of the block's rows, fetched while the tile is still being computed
-          for (uint32_t i = (uint32_t)etid; i < rows; i += kEpiThreads) {
-            const uint4 mraw = ld_cg_u4(&me.meta[(size_t)e * p.cap_rows + j + i]);
-            sc.tokw[i] = __uint_as_float(mraw.z);
-            // element offset of y[token, slot, 0] on the home rank (below 2^32: the launcher checks the size)
-            sc.tokdst[i] = make_uint2((mraw.x * (uint32_t)p.K + (mraw.y & 0xffu)) * (uint32_t)p.H, mraw.y >> 8);
-          }
-        }
-        uint32_t nsub[2];
-        fdmoe_split_rows(rows, &nsub[0], &nsub[1]);
-        bool ok = true;
-        uint32_t roff = 0u;
-        for (int sb = 0; sb < 2 && ok; ++sb) {
-          if (nsub[sb] == 0u) break;
-          // sub-block sb was accumulated in the next accumulator of the sequence
-          const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
-          ++tile_it;
-          ok = epi_vote_all(wait_bar_warp(p, sc, &sc.tmem_full[acc], aph, FDMOE_ERR_TIMEOUT_TMEM));
-          if (!ok) break;
-          if (p.prof && etid == 0 && sb == 0) pt1 = prof_now();
-          ptx::tcgen05_fence_after();
-          const uint32_t taddr = tmem_base + acc * kAccCols;
-          if (kind == FDMOE_TASK_FFN1)
-            ffn1_epilogue(p, sc, taddr, cta, q, h, lane, ewarp, e, n, j + roff, nsub[sb]);
-          else
-            ffn2_epilogue(p, sc, taddr, cta, q, h, lane, ewarp, n, roff, nsub[sb]);
-          ptx::tcgen05_fence_before();
-          __syncwarp();
-          if (lane == 0) acc_release(sc, cta, acc);
-          roff += nsub[sb];
-        }
-        if (!ok) break;
+        const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
+        ++tile_it;
+        stage_it += (kind == FDMOE_TASK_FFN1) ? nkb1 : nkb2;
+        if (!epi_vote_all(wait_bar(p, sc, &sc.tmem_full[acc], aph, FDMOE_ERR_TIMEOUT_TMEM))) break;
+        if (p.prof && etid == 0) pt1 = prof_now();
+        ptx::tcgen05_fence_after();
+        const uint32_t taddr = tmem_base + acc * kAccCols;
+        if (kind == FDMOE_TASK_FFN1)
+          ffn1_epilogue(p, sc, taddr, q, h, lane, ewarp, e, j, n, rows);
+        else
+          ffn2_epilogue(p, sc, taddr, q, h, lane, ewarp, e, j, n, rows);
+        ptx::tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&sc.tmem_empty[acc]);
         const uint32_t pta = (p.prof && etid == 0) ? prof_now() : 0u;
 
         // The tile's stores are issued.  Dependency counting, successor pushes and
@@ -1569,7 +1371,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         for (int tk = t_begin; tk < t_end && ok; ++tk) {
           for (int c0 = 0; c0 < p.H; c0 += kCombineCols, ++stage_it) {
             const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
-            ok = epi_vote_all(wait_bar_warp(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE));
+            ok = epi_vote_all(wait_bar(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE));
             if (!ok) break;
             const int nvec = min(kCombineCols, p.H - c0) / 8;
             if (etid < nvec) {
@@ -1598,13 +1400,17 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           }
         }
         if (!ok) break;
+        if (etid == 0) {
+          __threadfence_block();
+          sc.skip_done = sc.skip_done + 1u;
+        }
         if (etid == 0 && p.mode != 2) {
           fence_acqrel<false>();
           atomicAdd(&ctl->tokens_combined, (uint32_t)(t_end - t_begin));
           maybe_close(p);
         }
       } else if (kind == FDMOE_TASK_GATED) {
-        gated_task<S>(p, sc, etid);
+        gated_task<S>(sc.params, sc, etid);
       } else if (kind == FDMOE_TASK_TESTA || kind == FDMOE_TASK_TESTB) {
         // task-system self test: two dependent stages over a 256-element chunk
         int* ptr = p.test_buf + (size_t)j * kEpiThreads + etid;
@@ -1635,7 +1441,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       }
       if (etid == 0) prof_event(p, sc, kind, pt0, pt1, prof_now());
       __syncwarp();
-      if (lane == 0) ring_release(sc, cta, r);
+      if (lane == 0) ptx::mbar_arrive(&sc.ring_empty[r]);
     }
     if (etid == 0 && p.mode != 2) {
       // tell the completion warp that nothing more will come
@@ -1646,8 +1452,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       }
     }
   } else if (warp == kWarpTmem && p.mode != 2) {
-    // ---- completion warp: per finished tile half (each CTA of a pair reports its own),
-    // count it and publish what it unblocks
+    // ---- completion warp: per finished tile, count it and publish what it unblocks
     for (uint32_t it = 0;; ++it) {
       const uint32_t d = it % kDone, dph = (it / kDone) & 1u;
       int ok = 1;
@@ -1664,17 +1469,16 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       const FdmoeSlot t = sc.done_ring[d];
       const uint32_t kind = t.a & 0xffu;
       if (kind == FDMOE_TASK_EXIT) break;
-      const uint32_t e = (t.a >> 8) & 0xfffu, r0 = t.b, rows = t.c;
-      const size_t blk = (size_t)e * p.MT + r0 / FDMOE_TILE_M;  // blocks of one expert start at least 128 rows apart
+      const uint32_t e = (t.a >> 8) & 0xfffu, j = t.b, rows = t.c;
       if (kind == FDMOE_TASK_FFN1) {
         if (lane == 0) {
           if (!(p.debug_flags & 2)) fence_acqrel<false>();
-          const uint32_t prev = atomicAdd(&p.ffn1_done[blk], 1u);
-          if (prev == 2u * nt1 - 1u) {
+          const uint32_t prev = atomicAdd(&p.ffn1_done[(size_t)e * p.MT + j], 1u);
+          if (prev == nt1 - 1u) {
             if (!(p.debug_flags & 2)) fence_acqrel<false>();
             queue_push<false>(p, me, nt2, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
               a = task_word(FDMOE_TASK_FFN2, e, i);
-              b = r0;
+              b = j;
               c = rows;
             });
           }
@@ -1683,19 +1487,19 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         int last = 0;
         if (lane == 0) {
           if (!(p.debug_flags & 2)) fence_acqrel<S>();
-          const uint32_t prev = atomicAdd(&p.ffn2_done[blk], 1u);
+          const uint32_t prev = atomicAdd(&p.ffn2_done[(size_t)e * p.MT + j], 1u);
           if (!(p.debug_flags & 2)) fence_acqrel<S>();
-          last = prev == 2u * nt2 - 1u;
+          last = prev == nt2 - 1u;
         }
         last = __shfl_sync(0xffffffffu, last, 0);
         if (last) {
-          // every hidden-column tile of this block is stored: tell each home rank how many
-          // of its rows that makes (one counter update per home rank and block)
+          // every hidden-column tile of this m-tile is stored: tell each home rank how many
+          // of its rows that makes (one counter update per home rank and m-tile)
           uint32_t cnt[FDMOE_MAX_WORLD];
 #pragma unroll
           for (int w = 0; w < FDMOE_MAX_WORLD; ++w) cnt[w] = 0u;
           for (uint32_t r = lane; r < rows; r += 32) {
-            const uint4 mraw = ld_cg_u4(&me.meta[(size_t)e * p.cap_rows + r0 + r]);
+            const uint4 mraw = ld_cg_u4(&me.meta[(size_t)e * p.cap_rows + (size_t)j * 128 + r]);
             const int home = (int)mraw.y >> 8;
 #pragma unroll
             for (int w = 0; w < FDMOE_MAX_WORLD; ++w) cnt[w] += (home == w) ? 1u : 0u;
@@ -1714,7 +1518,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
             const uint32_t tl = (lane == p.rank) ? (uint32_t)p.T : ld_relaxed<S>(&hp.ctl->tokens_launch);
             if (prev + mine == tl * (uint32_t)p.K) th = tl;  // that home rank has all its rows
           }
-          // ranks completed by this block get their COMBINE tasks, published by the whole warp
+          // ranks completed by this m-tile get their COMBINE tasks, published by the whole warp
           uint32_t complete = __ballot_sync(0xffffffffu, th != 0u);
           while (complete) {
             const int home = __ffs(complete) - 1;
@@ -1759,14 +1563,11 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
     // shared memory and TMEM of this CTA are released
     const uint64_t t0 = ptx::globaltimer_ns();
     while (ptx::globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
   }
-  // neither CTA of a pair frees tensor memory or leaves while its partner may still signal
-  // its barriers or issue MMAs into its shared and tensor memory
-  ptx::tcgen05_fence_before();
-  ptx::cluster_sync();
   if (warp == kWarpTmem) {
     ptx::tcgen05_fence_after();
-    ptx::tmem_dealloc2(tmem_base, kTmemCols);
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
   if (tid == 0) {
     fence_acqrel<false>();
@@ -1800,26 +1601,6 @@ __global__ void cast_bf16_to_f32_kernel(const bf16* __restrict__ src, float* __r
 }  // namespace fdmoe
 
 // ======================================================== thin C ABI (host)
-namespace {
-// The kernel runs as clusters of two CTAs (one per SM), `grid` CTAs in all.
-template <bool S>
-cudaError_t launch_pairs(const FdmoeParams& params, int grid, cudaStream_t st) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(fdmoe::kThreads, 1, 1);
-  cfg.dynamicSmemBytes = (size_t)fdmoe::kSmemBytes;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, fdmoe::moe_persistent_kernel<S>, params);
-}
-}  // namespace
-
 extern "C" int fdmoe_kernel_prepare(int* smem_bytes_out, int* grid_out) {
   using namespace fdmoe;
   cudaError_t err;
@@ -1829,37 +1610,27 @@ extern "C" int fdmoe_kernel_prepare(int* smem_bytes_out, int* grid_out) {
   err = cudaFuncSetAttribute(moe_persistent_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemBytes);
   if (err != cudaSuccess) return (int)err;
-  int dev = 0, sms = 0;
+  int dev = 0, sms = 0, occ = 0;
   if ((err = cudaGetDevice(&dev)) != cudaSuccess) return (int)err;
   if ((err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess)
     return (int)err;
-  // one worker per SM, in pairs: as many clusters of two as the device can hold at once
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)(sms & ~1), 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = (size_t)kSmemBytes;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  int clusters = 0;
-  err = cudaOccupancyMaxActiveClusters(&clusters, moe_persistent_kernel<false>, &cfg);
+  err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, moe_persistent_kernel<false>, kThreads,
+                                                      kSmemBytes);
   if (err != cudaSuccess) return (int)err;
-  if (clusters < 1) return (int)cudaErrorLaunchOutOfResources;
-  const int grid = 2 * (clusters < sms / 2 ? clusters : sms / 2);
+  if (occ < 1) return (int)cudaErrorLaunchOutOfResources;
   if (smem_bytes_out) *smem_bytes_out = kSmemBytes;
-  if (grid_out) *grid_out = grid;
+  if (grid_out) *grid_out = sms;  // one worker per SM
   return 0;
 }
 
 extern "C" int fdmoe_kernel_launch(const FdmoeParams* params, int grid, void* stream) {
+  using namespace fdmoe;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (grid < 2 || (grid & 1)) return (int)cudaErrorInvalidValue;
-  const cudaError_t e = params->world > 1 ? launch_pairs<true>(*params, grid, st) : launch_pairs<false>(*params, grid, st);
-  return (int)(e != cudaSuccess ? e : cudaGetLastError());
+  if (params->world > 1)
+    moe_persistent_kernel<true><<<grid, kThreads, kSmemBytes, st>>>(*params);
+  else
+    moe_persistent_kernel<false><<<grid, kThreads, kSmemBytes, st>>>(*params);
+  return (int)cudaGetLastError();
 }
 
 extern "C" int fdmoe_cast_f32_to_bf16(const float* src, void* dst, uint64_t n, void* stream) {

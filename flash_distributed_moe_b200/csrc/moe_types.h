@@ -12,14 +12,9 @@ enum {
   FDMOE_MAX_TOPK = 8,
   FDMOE_MAX_EXPERTS = 128,
   FDMOE_MAX_HIDDEN = 4096,  // a token row is staged in shared memory by the exact gate path
-  // FFN tiles are computed by a pair of CTAs with the weights as the M operand (256 weight rows,
-  // 128 per CTA) and rows of one expert as the N operand (each MMA's rows split between the CTAs).
-  // A tile covers a "row block" of up to 512 rows as one or two sub-blocks of up to 256 rows (one
-  // MMA extent each) that share the weight operand.
-  FDMOE_TILE_M = 128,    // granule of an expert's row buffer (capacity, per-block counters)
-  FDMOE_BLOCK_ROWS = 512,  // most rows of one expert in one tile
-  FDMOE_TILE_N1 = 128,   // FFN1: activation columns per pair tile (256 weight rows: gate + up)
-  FDMOE_TILE_N2 = 256,   // FFN2: hidden columns per pair tile
+  FDMOE_TILE_M = 128,    // rows of one expert's packed buffer per GEMM tile
+  FDMOE_TILE_N1 = 128,   // FFN1: activation columns per tile (MMA N = 2 * 128: gate + up)
+  FDMOE_TILE_N2 = 256,   // FFN2: hidden columns per tile
   FDMOE_TILE_K = 64,     // one 128-byte swizzle atom of bf16 per stage
   FDMOE_GATE_TOKENS = 128,  // tokens per gate tile (one tcgen05 M tile)
   FDMOE_PACK_ROWS = 72,     // rows per PACK task (rows of one expert, sent by one rank)
@@ -28,8 +23,8 @@ enum {
 // Task kinds held by the global work queue.
 enum {
   FDMOE_TASK_NONE = 0,
-  FDMOE_TASK_FFN1 = 1,     // (expert, column tile, first row, rows): SwiGLU tile of one row block
-  FDMOE_TASK_FFN2 = 2,     // (expert, column tile, first row, rows): down-projection tile
+  FDMOE_TASK_FFN1 = 1,     // (expert, m_tile, n_tile, rows): SwiGLU tile
+  FDMOE_TASK_FFN2 = 2,     // (expert, m_tile, n_tile, rows): down-projection tile
   FDMOE_TASK_COMBINE = 3,  // (token group): ordered sum over the K slots
   FDMOE_TASK_GATED = 4,    // every rank has finished gating: row counts are final, start the dispatch
   FDMOE_TASK_TESTA = 5,    // task-system self test: x[i] *= 2 over a chunk, then push TESTB
@@ -57,9 +52,9 @@ enum {
 // holds the task of that ticket.
 typedef struct {
   uint32_t seq;
-  uint32_t a;  // kind | expert << 8 | column tile << 20
-  uint32_t b;  // first row of the block in the expert's buffer, or first token, or chunk index
-  uint32_t c;  // rows in the block, or tokens
+  uint32_t a;  // kind | expert << 8 | n_tile << 20
+  uint32_t b;  // m_tile, or token group, or chunk index
+  uint32_t c;  // valid rows in the tile
 } FdmoeSlot;
 
 // Sideband of one packed row (16 bytes): where its result goes.
@@ -118,10 +113,12 @@ typedef struct __attribute__((aligned(64))) {
 } FdmoeTensorMap;
 
 typedef struct {
-  FdmoeTensorMap tm_w13;       // [El][2][I][H] as a 5-D tensor; one box = 64 columns of 4 x (16 gate rows, the 16 up rows of the same features)
-  FdmoeTensorMap tm_w2;        // [El*H, I]          box 64 x 128
-  FdmoeTensorMap tm_x;         // [T, H]             box 64 x min(gate_rows, T)   (rebuilt per launch)
-  FdmoeTensorMap tm_gate;      // [E, H]             box 64 x min(64, E)
+  FdmoeTensorMap tm_packed;  // [El*cap_rows, H]   box 64 x 128
+  FdmoeTensorMap tm_w13;     // [El*2I, H]         box 64 x 128
+  FdmoeTensorMap tm_act;     // [El*cap_rows, I]   box 64 x 128
+  FdmoeTensorMap tm_w2;      // [El*H, I]          box 64 x 256
+  FdmoeTensorMap tm_x;       // [T, H]             box 64 x min(128, T)   (rebuilt per launch)
+  FdmoeTensorMap tm_gate;    // [E, H]             box 64 x min(128, E)
 
   FdmoePeer peers[FDMOE_MAX_WORLD];  // peers[rank] is this rank itself
 
@@ -133,17 +130,13 @@ typedef struct {
   int32_t MT;           // cap_rows / 128
   int32_t queue_mask;   // capacity - 1 (capacity is a power of two)
   int32_t combine_group;  // most tokens per COMBINE task
-  int32_t gate_rows;    // tokens per CTA of a GATE task: 32, 64 or 128 (rows of the CTA's 128-row half of the MMA tile that are used)
+  int32_t gate_rows;    // tokens per GATE task: 32, 64 or 128 (rows of the 128-row MMA tile that are used)
   int32_t mode;         // 0 full layer; 2 static tasks only (no gate)
   int32_t debug_flags;  // timing experiments only (results become invalid): 1 skip FFN stores,
                         // 2 skip completion fences, 4 skip proxy fences, 8 skip the operand loads of FFN tiles
   uint32_t expected_static;  // mode 2: tasks pre-filled by the host
   uint32_t epoch;       // launch counter (identical on all ranks)
   uint64_t timeout_ns;  // budget of every device-side wait
-
-  // Row-block operands: 16 descriptors each, in device memory; entry i has a box of 64 columns x 8(i+1) rows
-  const FdmoeTensorMap* tm_packed_rows;  // over the packed rows  [El*cap_rows, H]
-  const FdmoeTensorMap* tm_act_rows;     // over the activations  [El*cap_rows, I]
 
   const void* x;        // bf16 [T, H]
   void* out;            // bf16 [T, H] (may alias x)
@@ -177,18 +170,3 @@ int fdmoe_cast_bf16_to_f32(const void* src, float* dst, uint64_t n, void* stream
 #ifdef __cplusplus
 }
 #endif
-
-// Sub-blocks of a row block of `rows` rows (1..512): n0 rows (a multiple of 16 unless it is the
-// only sub-block) followed by n1 rows (0 if the block fits one MMA extent of 256 rows).
-#if defined(__CUDACC__)
-__host__ __device__
-#endif
-static inline void fdmoe_split_rows(uint32_t rows, uint32_t* n0, uint32_t* n1) {
-  if (rows <= 256u) {
-    *n0 = rows;
-    *n1 = 0u;
-  } else {
-    *n0 = ((rows + 1u) / 2u + 15u) & ~15u;
-    *n1 = rows - *n0;
-  }
-}

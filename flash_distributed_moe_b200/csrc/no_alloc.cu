@@ -135,8 +135,6 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   size_t off = AlignUp(L.total, 1024);
   const size_t off_act = off;
   off += AlignUp((size_t)g.El * g.cap_rows * g.I * 2, 1024);
-  const size_t off_maps = off;
-  off += AlignUp(sizeof(RowMaps), 256);
   const size_t off_idx = off;
   off += AlignUp((size_t)g.max_tokens_max * g.K * 4, 256);
   const size_t off_w = off;
@@ -160,15 +158,12 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
 
   FdmoeParams p;
   memset(&p, 0, sizeof(p));
-  {
-    RowMaps rows;
-    NA_CHECK(MakeStaticMaps(d->encode, &p, &rows, g, base + L.packed, base + off_act, ffn1ExpertWeights,
-                            ffn2ExpertWeights, gateWeights));
-    // pageable source: the copy has left `rows` when the call returns
-    NA_CHECK(cudaMemcpyAsync(base + off_maps, &rows, sizeof(RowMaps), cudaMemcpyHostToDevice, stream));
-    p.tm_packed_rows = reinterpret_cast<const RowMaps*>(base + off_maps)->packed;
-    p.tm_act_rows = reinterpret_cast<const RowMaps*>(base + off_maps)->act;
-  }
+  const uint64_t exp_rows = (uint64_t)g.El * g.cap_rows;
+  NA_CHECK(MakeTensorMap(d->encode, &p.tm_packed, base + L.packed, exp_rows, g.H, 128));
+  NA_CHECK(MakeTensorMap(d->encode, &p.tm_w13, ffn1ExpertWeights, (uint64_t)g.El * 2 * g.I, g.H, 128));
+  NA_CHECK(MakeTensorMap(d->encode, &p.tm_act, base + off_act, exp_rows, g.I, 128));
+  NA_CHECK(MakeTensorMap(d->encode, &p.tm_w2, ffn2ExpertWeights, (uint64_t)g.El * g.H, g.I, 256));
+  NA_CHECK(MakeTensorMap(d->encode, &p.tm_gate, gateWeights, (uint64_t)g.E, g.H, std::min(128, g.E)));
   p.gate_rows = tokensNum <= 32 * d->grid ? 32 : (tokensNum <= 64 * d->grid ? 64 : 128);
   if (tokensNum > 0)
     NA_CHECK(MakeTensorMap(d->encode, &p.tm_x, tokens, (uint64_t)tokensNum, g.H, std::min(p.gate_rows, tokensNum)));
