@@ -65,6 +65,12 @@ inline uint32_t QueueCapacity(const Geometry& g, int grid) {
   return NextPow2(tasks + 4ull * grid + 1024);
 }
 
+// Bytes of a rank's pack list: one 16-byte entry per PACK task; an expert's rows come in pieces of
+// FDMOE_PACK_ROWS with one ragged piece per expert.
+inline size_t PackListBytes(const Geometry& g, int max_tokens_local) {
+  return ((size_t)std::max(max_tokens_local, 1) * g.K / FDMOE_PACK_ROWS + g.E + 8) * 16;
+}
+
 inline ArenaLayout MakeLayout(const Geometry& g) {
   ArenaLayout L;
   size_t off = 0;

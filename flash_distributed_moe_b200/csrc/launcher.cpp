@@ -92,6 +92,7 @@ class MoeKernelLauncher final : public moe::IMoeKernelLauncher {
   float* topk_w_ = nullptr;
   int32_t* send_src_ = nullptr;  // this rank's send lists [E][maxTokens]
   int32_t* send_dst_ = nullptr;
+  uint32_t* pack_list_ = nullptr;  // this rank's PACK tasks of a launch in sending order
   uint32_t* status_host_ = nullptr;
   uint32_t* status_dev_ = nullptr;
   // fp32 I/O mode: bf16 copies of the weights and token staging
@@ -111,7 +112,7 @@ void MoeKernelLauncher::FreeAll() {
   for (int r = 0; r < (int)peer_bases_.size(); ++r)
     if (r != rank_ && peer_bases_[r]) cudaIpcCloseMemHandle(peer_bases_[r]);
   peer_bases_.clear();
-  void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, send_src_, send_dst_, gate_bf16_, w13_bf16_, w2_bf16_,
+  void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, send_src_, send_dst_, pack_list_, gate_bf16_, w13_bf16_, w2_bf16_,
                   tok_bf16_, out_bf16_, host_in_dev_, host_out_dev_, prof_, debug_logits_, stuck_};
   for (void* p : ptrs)
     if (p) cudaFree(p);
@@ -120,6 +121,7 @@ void MoeKernelLauncher::FreeAll() {
   topk_idx_ = nullptr;
   topk_w_ = nullptr;
   send_src_ = send_dst_ = nullptr;
+  pack_list_ = nullptr;
   gate_bf16_ = w13_bf16_ = w2_bf16_ = tok_bf16_ = out_bf16_ = host_in_dev_ = host_out_dev_ = nullptr;
   prof_ = nullptr;
   debug_logits_ = nullptr;
@@ -225,6 +227,7 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
     const size_t list_bytes = (size_t)g_.E * AlignUp((size_t)std::max(maxTokens, 1), 4) * 4 + 16;
     CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&send_src_), list_bytes));
     CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&send_dst_), list_bytes));
+    CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&pack_list_), PackListBytes(g_, maxTokens)));
   }
   CUDA_ERROR_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped));
   memset(status_host_, 0, 64);
@@ -318,6 +321,11 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   params_.topk_w = topk_w_;
   params_.send_src = send_src_;
   params_.send_dst = send_dst_;
+  params_.pack_list = pack_list_;
+  // PACK tasks outstanding at a time.  On one GPU packing is bound by memory writes and is fastest with
+  // every worker on it at once; across GPUs a window leaves workers for the FFN1 tiles of landed
+  // experts while rows are still crossing NVLink.
+  params_.pack_window = std::max(1, EnvInt("FLASHMOE_PACK_WINDOW", world > 1 ? 128 : (1 << 30)));
   params_.send_stride = (int32_t)AlignUp((size_t)std::max(maxTokens, 1), 4);
   params_.send_cnt = reinterpret_cast<uint32_t*>(arena_ + layout_.send_cnt);
   params_.ffn1_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn1_done);

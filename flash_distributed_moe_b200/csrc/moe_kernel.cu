@@ -48,7 +48,6 @@ constexpr int kStageB = 256 * FDMOE_TILE_K * 2;           // 32 KB
 constexpr int kStageBytes = kStageA + kStageB;            // 48 KB
 constexpr int kRing = 3;
 constexpr int kFixBlocks = 3;  // k-blocks of gate weights per stage in a GATEFIX task (3 x 16 KB)
-constexpr int kPrefetch = 8;  // k-blocks by which the L2 prefetch of weights runs ahead
 constexpr int kDone = 4;  // depth of the hand-off ring to the completion warp
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = 256;
@@ -747,6 +746,19 @@ __device__ __noinline__ bool pack_task(const FdmoeParams& p, SmemCtl& sc, uint8_
         st_relaxed<S>(&op.slots[(t0 + idx) & (uint32_t)p.queue_mask].seq, t0 + idx + 1u);
     }
   }
+  if (etid == 32) {
+    // this piece is done: the next entry of this rank's pack list may go out
+    FdmoeCtl* myctl = p.peers[p.rank].ctl;
+    const uint32_t nxt = atomicAdd(&myctl->pack_cursor, 1u);
+    if (nxt < ld_relaxed<false>(&myctl->pack_total)) {
+      const uint4 t = ld_cg_u4(reinterpret_cast<const uint4*>(p.pack_list) + nxt);
+      queue_push<false>(p, p.peers[p.rank], 1u, [&](uint32_t, uint32_t& a, uint32_t& b, uint32_t& c) {
+        a = t.x;
+        b = t.y;
+        c = t.z;
+      });
+    }
+  }
   epi_bar();  // sc.flag / sc.q_t0 may be rewritten by the next task only after everyone has read them
   return true;
 }
@@ -842,16 +854,22 @@ __device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uin
 // ============================================================ GATED and FFN
 // GATED: every rank has finished gating, so the row counts of this rank's
 // experts and this rank's send lists are final.  Records the number of m-tiles
-// this rank will process (termination), then publishes this rank's PACK tasks:
-// 64-row pieces of its send lists, expert by expert, starting with the experts
-// of the next rank so that the ranks do not all send to the same owner at once.
+// this rank will process (termination), then lays out this rank's PACK tasks
+// (pieces of FDMOE_PACK_ROWS rows of its send lists) in sending order and
+// publishes the first pack_window of them; every PACK task that finishes
+// publishes the next one, so that packing, whose pace is set by memory writes or
+// by NVLink, shares the workers with the FFN1 tiles of the experts that have
+// already landed.  Sending order: step i goes to local expert i / world of rank
+// (rank + 1 + i) % world, so that at every step the ranks send to different
+// owners and the experts of all ranks complete one after the other.
 template <bool S>
 __device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int etid) {
   const FdmoePeer& me = p.peers[p.rank];
   const int lane = etid & 31, w = etid >> 5;
   // (the task was taken from the queue with an acquire load ordered after every rank's reservations)
   uint32_t ntile = 0, npack = 0, ecnt = 0;
-  const int e_send = (etid < p.E) ? (int)(((uint32_t)((p.rank + 1) % p.world) * (uint32_t)p.El + (uint32_t)etid) % (uint32_t)p.E) : 0;
+  const int e_send =
+      (etid < p.E) ? ((p.rank + 1 + etid) % p.world) * p.El + etid / p.world : 0;
   if (etid < p.El) ntile = (ld_relaxed<S>(&me.expert_cnt[etid]) + 127u) / 128u;
   if (etid < p.E) {
     ecnt = __ldcg(&p.send_cnt[e_send]);
@@ -879,23 +897,34 @@ __device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int e
     total += sc.pre[i];
     mt += sc.pre[8 + i];
   }
+  const uint32_t window = min(total, (uint32_t)p.pack_window);
   if (etid == 0) {
-    sc.q_t0 = total ? atom_add<false>(&me.ctl->q_head, total) : 0u;
+    sc.q_t0 = window ? atom_add<false>(&me.ctl->q_head, window) : 0u;
     st_relaxed<false>(&me.ctl->mtiles_total, mt);
+    st_relaxed<false>(&me.ctl->pack_total, total);
+    st_relaxed<false>(&me.ctl->pack_cursor, window);
   }
+  // the pack list, in sending order
+  uint4* plist = reinterpret_cast<uint4*>(p.pack_list);
+  const uint32_t firstslot = off_pack + inc_pack - npack;  // exclusive prefix in sending order
+  for (uint32_t r = 0; r < npack; ++r)
+    plist[firstslot + r] = make_uint4(task_word(FDMOE_TASK_PACK, (uint32_t)e_send, 0u), r * FDMOE_PACK_ROWS,
+                                      min((uint32_t)FDMOE_PACK_ROWS, ecnt - r * FDMOE_PACK_ROWS), 0u);
   epi_bar();
   const uint32_t t0 = sc.q_t0;
-  const uint32_t firstslot = off_pack + inc_pack - npack;  // exclusive prefix in sending order
-  for (uint32_t r = 0; r < npack; ++r) {
-    FdmoeSlot* sl = &me.slots[(t0 + firstslot + r) & (uint32_t)p.queue_mask];
-    sl->a = task_word(FDMOE_TASK_PACK, (uint32_t)e_send, 0u);
-    sl->b = r * FDMOE_PACK_ROWS;
-    sl->c = min((uint32_t)FDMOE_PACK_ROWS, ecnt - r * FDMOE_PACK_ROWS);
+  bool any = false;
+  for (uint32_t idx = (uint32_t)etid; idx < window; idx += kEpiThreads) {
+    const uint4 t = ld_cg_u4(&plist[idx]);
+    FdmoeSlot* sl = &me.slots[(t0 + idx) & (uint32_t)p.queue_mask];
+    sl->a = t.x;
+    sl->b = t.y;
+    sl->c = t.z;
+    any = true;
   }
-  // one fence orders every payload above before every sequence word below
-  fence_acqrel<false>();
-  for (uint32_t r = 0; r < npack; ++r)
-    st_relaxed<false>(&me.slots[(t0 + firstslot + r) & (uint32_t)p.queue_mask].seq, t0 + firstslot + r + 1u);
+  // one fence orders every payload (and the list, the cursor and the totals) before every sequence word below
+  if (any || etid == 0) fence_acqrel<false>();
+  for (uint32_t idx = (uint32_t)etid; idx < window; idx += kEpiThreads)
+    st_relaxed<false>(&me.slots[(t0 + idx) & (uint32_t)p.queue_mask].seq, t0 + idx + 1u);
   epi_bar();
   if (etid == 0) {
     st_release<false>(&me.ctl->flush_done, 1u);
@@ -1169,17 +1198,10 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
               const int32_t brow = (int32_t)(e * 2u * (uint32_t)p.I + n * FDMOE_TILE_N1);
               ptx::tma_load_2d(sb, &p.tm_w13, &sc.full_bar[s], kx, brow);
               ptx::tma_load_2d(sb + kStageA, &p.tm_w13, &sc.full_bar[s], kx, brow + p.I);
-              // The weights come from HBM: ask L2 for them kPrefetch k-blocks ahead, so that the
-              // shared-memory stages only have to cover the L2 latency.
-              if (kb + kPrefetch < nkb) {
-                ptx::tma_prefetch_l2_2d(&p.tm_w13, kx + kPrefetch * FDMOE_TILE_K, brow);
-                ptx::tma_prefetch_l2_2d(&p.tm_w13, kx + kPrefetch * FDMOE_TILE_K, brow + p.I);
-              }
             } else {
               ptx::tma_load_2d(sa, &p.tm_act, &sc.full_bar[s], kx, arow);
               const int32_t brow = (int32_t)(e * (uint32_t)p.H + n * FDMOE_TILE_N2);
               ptx::tma_load_2d(sb, &p.tm_w2, &sc.full_bar[s], kx, brow);
-              if (kb + kPrefetch < nkb) ptx::tma_prefetch_l2_2d(&p.tm_w2, kx + kPrefetch * FDMOE_TILE_K, brow);
             }
           }
           if (!ok) break;

@@ -91,7 +91,9 @@ typedef struct {
   uint32_t tokens_combined;
   uint32_t tokens_launch;    // tokens of this rank this launch (written at kernel start)
   uint32_t executed;         // tasks finished (used only with expected_static)
-  uint32_t pad3[22];
+  uint32_t pack_total;       // PACK tasks of this rank this launch (entries of its pack list)
+  uint32_t pack_cursor;      // next entry of the pack list to publish
+  uint32_t pad3[20];
 } FdmoeCtl;
 
 // What one rank can reach of a peer (or of itself): all device pointers valid
@@ -149,6 +151,10 @@ typedef struct {
   int32_t* send_src;    // token << 4 | slot
   int32_t* send_dst;    // row in the owner's expert buffers
   int32_t send_stride;  // = max tokens of this rank (an expert gets at most one row per token)
+  // this rank's PACK tasks of the launch in sending order, {a, b, c, 0} each; `pack_window` of them
+  // are outstanding at a time (every finished PACK task publishes the next entry)
+  uint32_t* pack_list;
+  int32_t pack_window;
   uint32_t* ffn1_done;  // [El * MT]
   uint32_t* ffn2_done;  // [El * MT]
   uint32_t* status_host;  // mapped pinned word: first error code, readable without a sync

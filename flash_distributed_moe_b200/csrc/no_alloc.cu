@@ -143,6 +143,8 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   off += AlignUp((size_t)g.E * AlignUp((size_t)g.max_tokens_max, 4) * 4 + 16, 256);
   const size_t off_dst = off;
   off += AlignUp((size_t)g.E * AlignUp((size_t)g.max_tokens_max, 4) * 4 + 16, 256);
+  const size_t off_plist = off;
+  off += AlignUp(PackListBytes(g, g.max_tokens_max), 256);
   if (off > kScratchBytes) {
     MOE_ERROR_LOG("FlashMoeLaunchNoAlloc: this call needs %zu bytes of scratch, the fixed array holds %zu "
                   "(H=%d I=%d E=%d K=%d tokens=%d); use CreateLauncher/Launch for larger problems",
@@ -199,6 +201,8 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   p.send_cnt = reinterpret_cast<uint32_t*>(base + L.send_cnt);
   p.send_src = reinterpret_cast<int32_t*>(base + off_src);
   p.send_dst = reinterpret_cast<int32_t*>(base + off_dst);
+  p.pack_list = reinterpret_cast<uint32_t*>(base + off_plist);
+  p.pack_window = 1 << 30;
   p.send_stride = (int32_t)AlignUp((size_t)g.max_tokens_max, 4);
   p.ffn1_done = reinterpret_cast<uint32_t*>(base + L.ffn1_done);
   p.ffn2_done = reinterpret_cast<uint32_t*>(base + L.ffn2_done);
