@@ -76,6 +76,7 @@ class MoeKernelLauncher final : public moe::IMoeKernelLauncher {
  private:
   cudaError_t LaunchBf16(const void* tokens, void* output, int tokensNum, cudaStream_t stream, int mode,
                          uint32_t expected_static);
+  cudaError_t LaunchDevice(const void* tokens, void* output, int tokensNum, cudaStream_t stream);
   cudaError_t PrefillTasks(const std::vector<FdmoeSlot>& tasks, cudaStream_t stream);
   void FreeAll();
 
@@ -99,7 +100,20 @@ class MoeKernelLauncher final : public moe::IMoeKernelLauncher {
   void *gate_bf16_ = nullptr, *w13_bf16_ = nullptr, *w2_bf16_ = nullptr;
   void *tok_bf16_ = nullptr, *out_bf16_ = nullptr;
   // host-buffer entry point staging
-  void *host_in_dev_ = nullptr, *host_out_dev_ = nullptr;
+  // Two sets of device staging buffers and three internal streams (copy in, layer, copy out), so
+  // that consecutive calls overlap one call's copies with the other's kernel.
+  struct HostPipe {
+    void* in[2] = {nullptr, nullptr};
+    void* out[2] = {nullptr, nullptr};
+    cudaStream_t s_in = nullptr, s_run = nullptr, s_out = nullptr;
+    cudaEvent_t copied_in[2] = {nullptr, nullptr}, ran[2] = {nullptr, nullptr}, copied_out[2] = {nullptr, nullptr};
+    cudaEvent_t direct = nullptr;  // last Launch() made directly on a caller's stream
+    bool direct_pending = false;
+    uint64_t calls = 0;
+    bool ready = false;
+  } pipe_;
+  cudaError_t InitHostPipe();
+  void DestroyHostPipe();
   uint32_t* prof_ = nullptr;  // optional event trace (FLASHMOE_PROFILE=1)
   uint32_t* stuck_ = nullptr;  // per CTA and warp: where a role gave up waiting
   float* debug_logits_ = nullptr;  // optional gate-logit dump (FLASHMOE_DEBUG_LOGITS=1)
@@ -113,7 +127,8 @@ void MoeKernelLauncher::FreeAll() {
     if (r != rank_ && peer_bases_[r]) cudaIpcCloseMemHandle(peer_bases_[r]);
   peer_bases_.clear();
   void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, send_src_, send_dst_, pack_list_, gate_bf16_, w13_bf16_, w2_bf16_,
-                  tok_bf16_, out_bf16_, host_in_dev_, host_out_dev_, prof_, debug_logits_, stuck_};
+                  tok_bf16_, out_bf16_, pipe_.in[0], pipe_.in[1], pipe_.out[0], pipe_.out[1], prof_, debug_logits_,
+                  stuck_};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   arena_ = nullptr;
@@ -122,7 +137,8 @@ void MoeKernelLauncher::FreeAll() {
   topk_w_ = nullptr;
   send_src_ = send_dst_ = nullptr;
   pack_list_ = nullptr;
-  gate_bf16_ = w13_bf16_ = w2_bf16_ = tok_bf16_ = out_bf16_ = host_in_dev_ = host_out_dev_ = nullptr;
+  gate_bf16_ = w13_bf16_ = w2_bf16_ = tok_bf16_ = out_bf16_ = nullptr;
+  pipe_.in[0] = pipe_.in[1] = pipe_.out[0] = pipe_.out[1] = nullptr;
   prof_ = nullptr;
   debug_logits_ = nullptr;
   stuck_ = nullptr;
@@ -360,6 +376,7 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
 
 cudaError_t MoeKernelLauncher::Deinit(cudaStream_t stream) {
   cudaError_t first = cudaStreamSynchronize(stream);
+  DestroyHostPipe();  // drains the internal streams of the host-buffer entry point
   // no rank unmaps or frees while a peer may still be writing into its arena
   if (world_ > 1 && inited_) boot_.Barrier();
   FreeAll();
@@ -405,6 +422,20 @@ cudaError_t MoeKernelLauncher::Launch(const void* tokens, void* output, int toke
     return cudaErrorInvalidValue;
   }
   if (tokensNum > 0 && (!tokens || !output)) return cudaErrorInvalidValue;
+  if (pipe_.ready && stream != pipe_.s_run) {
+    // launches share the scratch arena: this one runs after the last one made through LaunchHost,
+    // and the next LaunchHost after this one
+    if (pipe_.calls) CUDA_ERROR_CHECK(cudaStreamWaitEvent(stream, pipe_.ran[(pipe_.calls - 1) & 1], 0));
+    const cudaError_t e = LaunchDevice(tokens, output, tokensNum, stream);
+    if (e != cudaSuccess) return e;
+    CUDA_ERROR_CHECK(cudaEventRecord(pipe_.direct, stream));
+    pipe_.direct_pending = true;
+    return cudaSuccess;
+  }
+  return LaunchDevice(tokens, output, tokensNum, stream);
+}
+
+cudaError_t MoeKernelLauncher::LaunchDevice(const void* tokens, void* output, int tokensNum, cudaStream_t stream) {
   if (dtype_ == moe::MOE_DTYPE_BF16) return LaunchBf16(tokens, output, tokensNum, stream, 0, 0);
   const uint64_t n = (uint64_t)tokensNum * g_.H;
   CUDA_ERROR_CHECK(fdmoe_cast_f32_to_bf16(static_cast<const float*>(tokens), tok_bf16_, n, stream));
@@ -412,20 +443,78 @@ cudaError_t MoeKernelLauncher::Launch(const void* tokens, void* output, int toke
   return static_cast<cudaError_t>(fdmoe_cast_bf16_to_f32(out_bf16_, static_cast<float*>(output), n, stream));
 }
 
+cudaError_t MoeKernelLauncher::InitHostPipe() {
+  const size_t esz = dtype_ == moe::MOE_DTYPE_FP32 ? 4 : 2;
+  const size_t cap = std::max<size_t>(16, (size_t)g_.max_tokens_local * g_.H * esz);
+  for (int i = 0; i < 2; ++i) {
+    CUDA_ERROR_CHECK(cudaMalloc(&pipe_.in[i], cap));
+    CUDA_ERROR_CHECK(cudaMalloc(&pipe_.out[i], cap));
+    CUDA_ERROR_CHECK(cudaEventCreateWithFlags(&pipe_.copied_in[i], cudaEventDisableTiming));
+    CUDA_ERROR_CHECK(cudaEventCreateWithFlags(&pipe_.ran[i], cudaEventDisableTiming));
+    CUDA_ERROR_CHECK(cudaEventCreateWithFlags(&pipe_.copied_out[i], cudaEventDisableTiming));
+  }
+  CUDA_ERROR_CHECK(cudaEventCreateWithFlags(&pipe_.direct, cudaEventDisableTiming));
+  CUDA_ERROR_CHECK(cudaStreamCreateWithFlags(&pipe_.s_in, cudaStreamNonBlocking));
+  CUDA_ERROR_CHECK(cudaStreamCreateWithFlags(&pipe_.s_run, cudaStreamNonBlocking));
+  CUDA_ERROR_CHECK(cudaStreamCreateWithFlags(&pipe_.s_out, cudaStreamNonBlocking));
+  pipe_.ready = true;
+  return cudaSuccess;
+}
+
+void MoeKernelLauncher::DestroyHostPipe() {
+  cudaStream_t* streams[] = {&pipe_.s_in, &pipe_.s_run, &pipe_.s_out};
+  for (cudaStream_t* st : streams)
+    if (*st) {
+      cudaStreamSynchronize(*st);
+      cudaStreamDestroy(*st);
+      *st = nullptr;
+    }
+  cudaEvent_t* events[] = {&pipe_.copied_in[0], &pipe_.copied_in[1], &pipe_.ran[0],   &pipe_.ran[1],
+                           &pipe_.copied_out[0], &pipe_.copied_out[1], &pipe_.direct};
+  for (cudaEvent_t* ev : events)
+    if (*ev) {
+      cudaEventDestroy(*ev);
+      *ev = nullptr;
+    }
+  pipe_.ready = false;
+  pipe_.calls = 0;
+  pipe_.direct_pending = false;
+}
+
+// Host buffers in, host buffers out.  The input must be complete in host memory when the call is
+// made; the result is complete once `stream` has reached this point (synchronise it, or order
+// later work after it).  Copy in, layer and copy out run on internal streams with two sets of
+// staging buffers: back-to-back calls overlap the copies of one with the kernel of the other, so a
+// stream of calls runs at the pace of the slowest of the three.
 cudaError_t MoeKernelLauncher::LaunchHost(const void* hostTokens, void* hostOutput, int tokensNum,
                                           cudaStream_t stream) {
   if (!inited_) return cudaErrorNotReady;
   if (tokensNum < 0 || tokensNum > g_.max_tokens_local) return cudaErrorInvalidValue;
+  if (tokensNum > 0 && (!hostTokens || !hostOutput)) return cudaErrorInvalidValue;
+  if (!pipe_.ready) CUDA_ERROR_CHECK(InitHostPipe());
   const size_t esz = dtype_ == moe::MOE_DTYPE_FP32 ? 4 : 2;
   const size_t bytes = (size_t)tokensNum * g_.H * esz;
-  if (!host_in_dev_) {
-    const size_t cap = std::max<size_t>(16, (size_t)g_.max_tokens_local * g_.H * esz);
-    CUDA_ERROR_CHECK(cudaMalloc(&host_in_dev_, cap));
-    CUDA_ERROR_CHECK(cudaMalloc(&host_out_dev_, cap));
+  const int slot = (int)(pipe_.calls & 1);
+  const bool reused = pipe_.calls >= 2;
+  // copy in: the staging buffer is free once the kernel of two calls ago has run
+  if (reused) CUDA_ERROR_CHECK(cudaStreamWaitEvent(pipe_.s_in, pipe_.ran[slot], 0));
+  if (bytes) CUDA_ERROR_CHECK(cudaMemcpyAsync(pipe_.in[slot], hostTokens, bytes, cudaMemcpyHostToDevice, pipe_.s_in));
+  CUDA_ERROR_CHECK(cudaEventRecord(pipe_.copied_in[slot], pipe_.s_in));
+  // layer: after its input has arrived, the result buffer has been copied out, and any launch made directly
+  CUDA_ERROR_CHECK(cudaStreamWaitEvent(pipe_.s_run, pipe_.copied_in[slot], 0));
+  if (reused) CUDA_ERROR_CHECK(cudaStreamWaitEvent(pipe_.s_run, pipe_.copied_out[slot], 0));
+  if (pipe_.direct_pending) {
+    CUDA_ERROR_CHECK(cudaStreamWaitEvent(pipe_.s_run, pipe_.direct, 0));
+    pipe_.direct_pending = false;
   }
-  if (bytes) CUDA_ERROR_CHECK(cudaMemcpyAsync(host_in_dev_, hostTokens, bytes, cudaMemcpyHostToDevice, stream));
-  CUDA_ERROR_CHECK(Launch(host_in_dev_, host_out_dev_, tokensNum, stream));
-  if (bytes) CUDA_ERROR_CHECK(cudaMemcpyAsync(hostOutput, host_out_dev_, bytes, cudaMemcpyDeviceToHost, stream));
+  CUDA_ERROR_CHECK(LaunchDevice(pipe_.in[slot], pipe_.out[slot], tokensNum, pipe_.s_run));
+  CUDA_ERROR_CHECK(cudaEventRecord(pipe_.ran[slot], pipe_.s_run));
+  // copy out, then the caller's stream joins
+  CUDA_ERROR_CHECK(cudaStreamWaitEvent(pipe_.s_out, pipe_.ran[slot], 0));
+  if (bytes) CUDA_ERROR_CHECK(cudaMemcpyAsync(hostOutput, pipe_.out[slot], bytes, cudaMemcpyDeviceToHost, pipe_.s_out));
+  CUDA_ERROR_CHECK(cudaEventRecord(pipe_.copied_out[slot], pipe_.s_out));
+  CUDA_ERROR_CHECK(cudaStreamWaitEvent(stream, pipe_.copied_out[slot], 0));
+  ++pipe_.calls;
   return cudaSuccess;
 }
 
@@ -459,6 +548,7 @@ cudaError_t MoeKernelLauncher::DebugRead(int which, void* dst, size_t offset, si
 // Writes tasks into the queue from the host (mode 2 launches only).
 cudaError_t MoeKernelLauncher::PrefillTasks(const std::vector<FdmoeSlot>& tasks, cudaStream_t stream) {
   CUDA_ERROR_CHECK(cudaStreamSynchronize(stream));
+  if (pipe_.ready) CUDA_ERROR_CHECK(cudaStreamSynchronize(pipe_.s_run));
   FdmoeCtl ctl;
   CUDA_ERROR_CHECK(cudaMemcpy(&ctl, arena_ + layout_.ctl, sizeof(ctl), cudaMemcpyDeviceToHost));
   const uint32_t head = ctl.q_head;

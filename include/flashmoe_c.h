@@ -42,9 +42,12 @@ int FlashMoeCreate(FlashMoeHandle* out, const void* gateWeights, const void* ffn
 int FlashMoeLaunch(FlashMoeHandle h, const void* tokens, void* output, int tokensNum, void* stream);
 
 /* Launch with HOST buffers: copies `tokens` to the device, runs the layer and
- * copies the result back, all on `stream`; returns after enqueueing (pinned
- * host memory) or after the copies (pageable memory).  The reference's tests do
- * the same three steps by hand (test/singleGPU/cpp/moe/moeTest.cpp:38-56). */
+ * copies the result back.  The input must be complete in host memory when the
+ * call is made; the result is complete once `stream` has reached this point.
+ * Returns after enqueueing (pinned host memory).  The three steps run on
+ * internal streams with two sets of staging buffers, so back-to-back calls
+ * overlap the copies of one call with the kernel of the other.  The reference's
+ * tests do the same three steps by hand (test/singleGPU/cpp/moe/moeTest.cpp:38-56). */
 int FlashMoeLaunchHost(FlashMoeHandle h, const void* hostTokens, void* hostOutput, int tokensNum,
                        void* stream);
 
