@@ -1,19 +1,20 @@
 // The persistent MoE-layer kernel for sm_100a and its thin C ABI.
 //
 // One CTA per SM, every CTA a worker that pulls tasks from a ticket-based global
-// queue and overlaps four kinds of work:
-//   GATE    128-token tile: gate GEMM on tcgen05, top-k, fp64 softmax, row
-//           reservation in the owners' expert buffers (tokens whose leading
-//           logits are nearly tied are recomputed with fp32 FMAs in the
-//           reference's accumulation order, so the selection is the reference's);
-//   GATED   all ranks have gated: publishes this rank's PACK tasks, expert by expert;
-//   PACK    64 rows of one expert: copies them into the owner's expert buffer; the
-//           sender that completes an expert publishes its FFN1 tiles;
+// queue and overlaps these kinds of work:
+//   GATE    token tile: gate GEMM on tcgen05, top-k, softmax, row reservation in
+//           the owners' expert buffers and entries in this rank's per-expert send
+//           lists (tokens whose leading logits are nearly tied are recomputed by a
+//           GATEFIX task with fp32 FMAs in the reference's accumulation order, so
+//           the selection is the reference's);
+//   GATED   all ranks have gated: lays out this rank's PACK tasks, expert by expert;
+//   PACK    up to 72 rows of one expert: bulk copies into the owner's expert buffer;
+//           the sender that completes an expert publishes its FFN1 tiles;
 //   FFN1/2  128-row expert tiles on tcgen05 with TMEM accumulators fed by TMA
 //           (SwiGLU epilogue; routing-weight epilogue stored on the home rank);
 //   COMBINE token group: ordered sum of the K weighted rows.
-// Cross-GPU traffic is plain stores and scoped atomics into peers' symmetric
-// buffers.
+// Cross-GPU traffic is plain stores, bulk stores and scoped atomics into peers'
+// symmetric buffers.
 //
 // Counterparts in the reference project (HIP, MI300X):
 //   persistent kernel + phases     src/hip/kernel/moeKernel.h:37-107
@@ -571,16 +572,17 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
   epi_bar();
   prof_mark(p, sc, etid, 3);
   if (etid < nt && !sc.isflag[etid]) {
-    // softmax over the K kept logits, in double, in the reference's order: the
-    // values are descending, so the running max is the first one and the sum is
-    // 1 + e_1 + e_2 + ... (reference refSoftmax.h:23-50)
-    const double m = (double)sc.top_v[etid][0];
-    double ex[FDMOE_MAX_TOPK];
-    double sum = 1.0;
+    // softmax over the K kept logits in the reference's order: the values are descending, so
+    // the running max is the first one and the sum is 1 + e_1 + e_2 + ... (reference
+    // refSoftmax.h:23-50, which works in double; fp32 with the accurate expf stays within 3e-7 of
+    // it, far inside the 1e-5 the routing weights are held to, and costs a tenth of the time)
+    const float m = sc.top_v[etid][0];
+    float ex[FDMOE_MAX_TOPK];
+    float sum = 1.0f;
 #pragma unroll
     for (int k = 0; k < FDMOE_MAX_TOPK; ++k) {
       if (k < K) {
-        ex[k] = exp((double)sc.top_v[etid][k] - m);
+        ex[k] = expf(sc.top_v[etid][k] - m);
         if (k > 0) sum += ex[k];
       }
     }
@@ -588,7 +590,7 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
     for (int k = 0; k < FDMOE_MAX_TOPK; ++k) {
       if (k < K) {
         const int e = sc.top_i[etid][k];
-        const float w = (float)(ex[k] / sum);
+        const float w = ex[k] / sum;
         sc.tk_w[etid][k] = w;
         sc.lpos[etid][k] = (uint8_t)atomicAdd(&sc.cnt[e], 1u);
         p.topk_idx[(size_t)(t0 + etid) * K + k] = e;
@@ -822,13 +824,13 @@ __device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uin
     float myv;
     int myi;
     topk_warp(sc.exact[half], E, K, lane, myv, myi);
-    // softmax in double in the reference's order (refSoftmax.h:23-50)
-    const double m = (double)__shfl_sync(0xffffffffu, myv, 0);
-    const double ex = (lane < K) ? exp((double)myv - m) : 0.0;
-    double sum = 1.0;
+    // softmax in the reference's order (refSoftmax.h:23-50), in fp32 as in the GATE task
+    const float m = __shfl_sync(0xffffffffu, myv, 0);
+    const float ex = (lane < K) ? expf(myv - m) : 0.0f;
+    float sum = 1.0f;
     for (int j = 1; j < K; ++j) sum += __shfl_sync(0xffffffffu, ex, j);
     if (lane < K) {
-      const float w = (float)(ex / sum);
+      const float w = ex / sum;
       const int owner = myi / p.El, le = myi - owner * p.El;
       const uint32_t pos = atom_add<S>(&p.peers[owner].expert_cnt[le], 1u);
       if (pos >= (uint32_t)p.cap_rows) {
@@ -1036,6 +1038,12 @@ __device__ __forceinline__ void ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc,
 // pieces of up to 2048 columns: stage layout [K][piece], 4 KB per slot row.
 constexpr int kCombineCols = 2048;
 
+// k-blocks a tile task puts into one pipeline stage: two for GATE tiles of up to 64 tokens
+// (H is a multiple of 256, so the number of k-blocks is even), one otherwise.
+__device__ __forceinline__ uint32_t gate_kblocks_per_stage(bool is_gate, int gate_rows) {
+  return (is_gate && gate_rows <= 64) ? 2u : 1u;
+}
+
 template <bool S>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
@@ -1176,9 +1184,12 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           const int32_t arow = gt ? (int32_t)(j * (uint32_t)p.gate_rows) : (int32_t)(e * (uint32_t)p.cap_rows + j * 128u);
           // bytes one GATE stage receives: both boxes are clamped to the tensor extents
           const uint32_t gate_bytes = (uint32_t)(min(p.gate_rows, p.T) + min(128, p.E)) * FDMOE_TILE_K * 2u;
+          // GATE tiles of up to 64 tokens are bound by the round trip of a stage, not by its size:
+          // they put two k-blocks into one stage (A 2 x 8 KB, B 2 x 16 KB)
+          const uint32_t gk = gate_kblocks_per_stage(gt, p.gate_rows);
           ptx::fence_proxy_async();  // rows / activations were written with generic stores
           bool ok = true;
-          for (uint32_t kb = 0; kb < nkb && ok; ++kb, ++stage_it) {
+          for (uint32_t kb = 0; kb < nkb && ok; kb += gk, ++stage_it) {
             const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
             ok = wait_bar(p, sc, &sc.empty_bar[s], sph ^ 1u, FDMOE_ERR_TIMEOUT_STAGE);
             if (!ok) break;
@@ -1188,11 +1199,13 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
               ptx::mbar_arrive(&sc.full_bar[s]);
               continue;
             }
-            ptx::mbar_expect_tx(&sc.full_bar[s], gt ? gate_bytes : (uint32_t)kStageBytes);
+            ptx::mbar_expect_tx(&sc.full_bar[s], gt ? gk * gate_bytes : (uint32_t)kStageBytes);
             const int32_t kx = (int32_t)(kb * FDMOE_TILE_K);
             if (gt) {
-              ptx::tma_load_2d(sa, &p.tm_x, &sc.full_bar[s], kx, arow);
-              ptx::tma_load_2d(sb, &p.tm_gate, &sc.full_bar[s], kx, 0);
+              for (uint32_t i = 0; i < gk; ++i) {
+                ptx::tma_load_2d(sa + i * (kStageA / 2), &p.tm_x, &sc.full_bar[s], kx + (int32_t)(i * FDMOE_TILE_K), arow);
+                ptx::tma_load_2d(sb + i * kStageA, &p.tm_gate, &sc.full_bar[s], kx + (int32_t)(i * FDMOE_TILE_K), 0);
+              }
             } else if (f1) {
               ptx::tma_load_2d(sa, &p.tm_packed, &sc.full_bar[s], kx, arow);
               const int32_t brow = (int32_t)(e * 2u * (uint32_t)p.I + n * FDMOE_TILE_N1);
@@ -1265,19 +1278,23 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           if (!wait_bar(p, sc, &sc.tmem_empty[acc], aph ^ 1u, FDMOE_ERR_TIMEOUT_TMEM)) break;
           ptx::tcgen05_fence_after();
           const uint32_t d_tmem = tmem_base + acc * kAccCols;
+          const uint32_t gk = gate_kblocks_per_stage(kind == FDMOE_TASK_GATE, p.gate_rows);
           bool ok = true;
-          for (uint32_t kb = 0; kb < nkb; ++kb, ++stage_it) {
+          for (uint32_t kb = 0; kb < nkb; kb += gk, ++stage_it) {
             const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
             ok = wait_bar(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE);
             if (!ok) break;
             ptx::tcgen05_fence_after();
             const uint32_t sa = ptx::smem_u32(stage + s * kStageBytes);
-            const uint64_t da = ptx::make_smem_desc_sw128(sa);
-            const uint64_t db = ptx::make_smem_desc_sw128(sa + kStageA);
+            for (uint32_t i = 0; i < gk; ++i) {
+              // (a GATE stage with two k-blocks: A at 8 KB, B at 16 KB steps)
+              const uint64_t da = ptx::make_smem_desc_sw128(sa + i * (kStageA / 2));
+              const uint64_t db = ptx::make_smem_desc_sw128(sa + kStageA + i * kStageA);
 #pragma unroll
-            for (uint32_t k4 = 0; k4 < FDMOE_TILE_K / 16; ++k4) {
-              // +32 bytes per 16-element k step inside the 128-byte swizzle row
-              ptx::umma_bf16(d_tmem, da + k4 * 2u, db + k4 * 2u, idesc, (kb | k4) != 0u);
+              for (uint32_t k4 = 0; k4 < FDMOE_TILE_K / 16; ++k4) {
+                // +32 bytes per 16-element k step inside the 128-byte swizzle row
+                ptx::umma_bf16(d_tmem, da + k4 * 2u, db + k4 * 2u, idesc, (kb | i | k4) != 0u);
+              }
             }
             ptx::umma_commit(&sc.empty_bar[s]);  // frees the stage when the MMAs have read it
           }
@@ -1336,7 +1353,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       if (kind == FDMOE_TASK_GATE) {
         const uint32_t acc = tile_it & 1u, aph = (tile_it >> 1) & 1u;
         ++tile_it;
-        stage_it += nkb1;
+        stage_it += nkb1 / gate_kblocks_per_stage(true, p.gate_rows);
         if (!epi_vote_all(wait_bar(p, sc, &sc.tmem_full[acc], aph, FDMOE_ERR_TIMEOUT_TMEM))) break;
         if (p.prof && etid == 0) pt1 = prof_now();
         ptx::tcgen05_fence_after();

@@ -101,8 +101,10 @@ class MoeKernelLauncher:
         _lib.check(code, "Launch")
 
     def launch_host(self, tokens: torch.Tensor, output: torch.Tensor) -> None:
-        """Host-buffer entry point: `tokens`/`output` are CPU tensors (pinned for an asynchronous call);
-        the library copies in, runs and copies out on the current stream."""
+        """Host-buffer entry point: `tokens`/`output` are CPU tensors (pinned for an asynchronous call).
+        `tokens` must be complete when the call is made; `output` is complete once the current stream
+        has reached this point.  The library copies in, runs and copies out on internal streams, so
+        calls made back to back overlap the copies of one with the kernel of the other."""
         if not self.valid:
             raise RuntimeError("Launcher was destroyed")
         if tokens.is_cuda or output.is_cuda or tokens.dtype != self._dtype or output.dtype != self._dtype:

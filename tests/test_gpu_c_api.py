@@ -69,6 +69,32 @@ def test_host_buffer_entry_point_matches_device_entry_point():
         layer.close()
 
 
+def test_host_entry_point_pipelines_back_to_back_calls():
+    # calls made back to back overlap the copies of one with the kernel of the other (two sets of
+    # staging buffers on internal streams); device-pointer launches in between share the scratch
+    # arena and must stay ordered with them
+    s = synth.TINY
+    gate, w13, w2 = synth.make_weights(s, std=0.05)
+    layer = tl.GpuLayer(s, gate, w13, w2, max_tokens=64)
+    try:
+        xs = [synth.make_tokens(s, T, seed=20 + i) for i, T in enumerate((64, 17, 0, 50, 64, 33))]
+        want = [layer.run(x).cpu() for x in xs]
+        ins = [x.clone().pin_memory() for x in xs]
+        outs = [torch.empty_like(x).pin_memory() for x in ins]
+        dev_x = xs[3].cuda()
+        dev_out = torch.empty_like(dev_x)
+        for i, (xin, out) in enumerate(zip(ins, outs)):
+            layer.launcher.launch_host(xin, out)
+            if i == 2:
+                layer.launcher.launch(dev_x, dev_out)  # a direct launch in the middle of the pipeline
+        torch.cuda.synchronize()
+        for i, (out, ref) in enumerate(zip(outs, want)):
+            assert torch.equal(out, ref), i
+        assert torch.equal(dev_out.cpu(), want[3])
+    finally:
+        layer.close()
+
+
 def test_fp32_io_adapter():
     # the reference interface is fp32; weights are converted once, tokens/output cast at the boundary
     s = synth.TINY

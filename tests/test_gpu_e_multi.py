@@ -57,3 +57,8 @@ def test_two_ranks_qwen3_30b_shape():
 
 def test_four_ranks_uneven_tokens():
     run_ranks("tiny", [3, 50, 0, 129])
+
+
+def test_eight_ranks_qwen3_30b_shape():
+    # every rank owns 16 of the 128 experts; uneven token counts, one rank without tokens
+    run_ranks("qwen", [96, 17, 0, 130, 64, 1, 200, 33])
