@@ -72,7 +72,7 @@ struct __align__(64) SmemCtl {
   uint32_t q_total;
   uint32_t prof_n;
   uint32_t n_flagged;
-  uint32_t pre[16];  // flush scratch: per-warp totals
+  uint32_t pre[16];  // GATED scratch: per-warp totals
   // Copy of the kernel parameters for the task bodies that are compiled as separate functions:
   // there the parameter block is only reachable through a generic pointer, and every access to
   // the constant bank through one costs on the order of a hundred cycles; shared memory does not.
@@ -354,14 +354,14 @@ __device__ __forceinline__ FdmoeSlot queue_pop(const FdmoeParams& p, SmemCtl& sc
   return out;
 }
 
-// Closes this rank's queue once the flush has run, every m-tile of its experts
+// Closes this rank's queue once GATED has run, every m-tile of its experts
 // has finished FFN2 and every token of this rank has been combined.  Called
 // after each of those three kinds of event; the sequentially-consistent fence
 // guarantees that the last caller sees the other two conditions.
 __device__ __forceinline__ void maybe_close(const FdmoeParams& p) {
   FdmoeCtl* ctl = p.peers[p.rank].ctl;
   fence_sc<false>();
-  if (ld_relaxed<false>(&ctl->flush_done) == 0u) return;
+  if (ld_relaxed<false>(&ctl->gated_done) == 0u) return;
   if (ld_relaxed<false>(&ctl->mtiles_done) != ld_relaxed<false>(&ctl->mtiles_total)) return;
   if (ld_relaxed<false>(&ctl->tokens_combined) != ld_relaxed<false>(&ctl->tokens_launch)) return;
   st_release<false>(&ctl->closed, 1u);
@@ -929,7 +929,7 @@ __device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int e
     st_relaxed<false>(&me.slots[(t0 + idx) & (uint32_t)p.queue_mask].seq, t0 + idx + 1u);
   epi_bar();
   if (etid == 0) {
-    st_release<false>(&me.ctl->flush_done, 1u);
+    st_release<false>(&me.ctl->gated_done, 1u);
     maybe_close(p);
   }
 }

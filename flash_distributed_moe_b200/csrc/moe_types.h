@@ -85,7 +85,7 @@ typedef struct {
   uint32_t gated_tokens;     // tokens of this rank whose routing is decided
   uint32_t rows_arrived;     // weighted rows of this rank's tokens that have come back (T*K when complete)
   uint32_t ranks_gated;      // ranks whose gating is finished (incl. this one)
-  uint32_t flush_done;
+  uint32_t gated_done;        // the GATED task of this launch has run (tile total and pack list are set)
   uint32_t mtiles_total;     // m-tiles of this rank's experts this launch
   uint32_t mtiles_done;      // m-tiles whose FFN2 is complete
   uint32_t tokens_combined;
