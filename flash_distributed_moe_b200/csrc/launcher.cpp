@@ -303,8 +303,8 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_packed, arena_ + layout_.packed, exp_rows, g_.H, 128));
   CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_w13, w13_dev, (uint64_t)g_.El * 2 * g_.I, g_.H, 128));
   CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_act, act_, exp_rows, g_.I, 128));
-  CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_w2, w2_dev, (uint64_t)g_.El * g_.H, g_.I, 128));
-  CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_gate, gate_dev, (uint64_t)g_.E, g_.H, std::min(64, g_.E)));
+  CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_w2, w2_dev, (uint64_t)g_.El * g_.H, g_.I, 256));
+  CUDA_ERROR_CHECK(MakeTensorMap(enc, &params_.tm_gate, gate_dev, (uint64_t)g_.E, g_.H, std::min(128, g_.E)));
   encode_ = enc;
   for (int r = 0; r < world; ++r) {
     uint8_t* b = static_cast<uint8_t*>(peer_bases_[r]);
@@ -593,14 +593,10 @@ cudaError_t MoeKernelLauncher::TestQueueGemm(const uint32_t* rowsPerExpert, cons
     for (uint32_t r = 0; r < rows; ++r) meta[r] = FdmoeRowMeta{(int32_t)(row0 + r), rank_ << 8, 1.0f, 0};
     CUDA_ERROR_CHECK(cudaMemcpy(arena_ + layout_.meta + (size_t)e * g_.cap_rows * sizeof(FdmoeRowMeta), meta.data(),
                                 rows * sizeof(FdmoeRowMeta), cudaMemcpyHostToDevice));
-    // one task per pair of row tiles (2jp, 2jp + 1) and column tile
-    for (uint32_t jp = 0; jp * 256 < rows; ++jp)
-      for (uint32_t n = 0; n < nt2; ++n) {
-        const uint32_t rows0 = std::min<uint32_t>(128, rows - jp * 256);
-        const uint32_t rows1 = rows > jp * 256 + 128 ? std::min<uint32_t>(128, rows - jp * 256 - 128) : 0;
-        tasks.push_back(FdmoeSlot{0, (uint32_t)FDMOE_TASK_FFN2 | ((uint32_t)e << 8) | (n << 20), jp,
-                                  rows0 | (rows1 << 16)});
-      }
+    for (uint32_t j = 0; j * 128 < rows; ++j)
+      for (uint32_t n = 0; n < nt2; ++n)
+        tasks.push_back(FdmoeSlot{0, (uint32_t)FDMOE_TASK_FFN2 | ((uint32_t)e << 8) | (n << 20), j,
+                                  std::min<uint32_t>(128, rows - j * 128)});
     row0 += rows;
   }
   if (tasks.size() + 1024 > g_.queue_cap) return cudaErrorInvalidValue;
@@ -610,8 +606,7 @@ cudaError_t MoeKernelLauncher::TestQueueGemm(const uint32_t* rowsPerExpert, cons
   void* saved_y = params_.peers[rank_].ystage;
   params_.K = 1;
   params_.peers[rank_].ystage = out;
-  // both CTAs of a pair report a finished task
-  const cudaError_t e = LaunchBf16(nullptr, nullptr, 0, stream, 2, (uint32_t)tasks.size() * 2u);
+  const cudaError_t e = LaunchBf16(nullptr, nullptr, 0, stream, 2, (uint32_t)tasks.size());
   params_.K = saved_k;
   params_.peers[rank_].ystage = saved_y;
   return e;

@@ -23,8 +23,8 @@ enum {
 // Task kinds held by the global work queue.
 enum {
   FDMOE_TASK_NONE = 0,
-  FDMOE_TASK_FFN1 = 1,     // (expert, pair of row tiles, column tile, rows): SwiGLU tiles of a CTA pair
-  FDMOE_TASK_FFN2 = 2,     // (expert, pair of row tiles, column tile, rows): down-projection tiles
+  FDMOE_TASK_FFN1 = 1,     // (expert, m_tile, n_tile, rows): SwiGLU tile
+  FDMOE_TASK_FFN2 = 2,     // (expert, m_tile, n_tile, rows): down-projection tile
   FDMOE_TASK_COMBINE = 3,  // (token group): ordered sum over the K slots
   FDMOE_TASK_GATED = 4,    // every rank has finished gating: row counts are final, start the dispatch
   FDMOE_TASK_TESTA = 5,    // task-system self test: x[i] *= 2 over a chunk, then push TESTB
@@ -53,8 +53,8 @@ enum {
 typedef struct {
   uint32_t seq;
   uint32_t a;  // kind | expert << 8 | n_tile << 20
-  uint32_t b;  // pair of row tiles (tiles 2b and 2b + 1 of the expert), or first token, or chunk index
-  uint32_t c;  // rows of tile 2b | rows of tile 2b + 1 << 16, or token count
+  uint32_t b;  // m_tile, or token group, or chunk index
+  uint32_t c;  // valid rows in the tile
 } FdmoeSlot;
 
 // Sideband of one packed row (16 bytes): where its result goes.
@@ -116,11 +116,11 @@ typedef struct __attribute__((aligned(64))) {
 
 typedef struct {
   FdmoeTensorMap tm_packed;  // [El*cap_rows, H]   box 64 x 128
-  FdmoeTensorMap tm_w13;     // [El*2I, H]         box 64 x 128 (the gate rows or the up rows of a column tile)
+  FdmoeTensorMap tm_w13;     // [El*2I, H]         box 64 x 128
   FdmoeTensorMap tm_act;     // [El*cap_rows, I]   box 64 x 128
-  FdmoeTensorMap tm_w2;      // [El*H, I]          box 64 x 128 (a CTA's half of the 256-column tile)
+  FdmoeTensorMap tm_w2;      // [El*H, I]          box 64 x 256
   FdmoeTensorMap tm_x;       // [T, H]             box 64 x min(128, T)   (rebuilt per launch)
-  FdmoeTensorMap tm_gate;    // [E, H]             box 64 x min(64, E) (a CTA's half of the experts)
+  FdmoeTensorMap tm_gate;    // [E, H]             box 64 x min(128, E)
 
   FdmoePeer peers[FDMOE_MAX_WORLD];  // peers[rank] is this rank itself
 

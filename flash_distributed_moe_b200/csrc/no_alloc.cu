@@ -164,8 +164,8 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   NA_CHECK(MakeTensorMap(d->encode, &p.tm_packed, base + L.packed, exp_rows, g.H, 128));
   NA_CHECK(MakeTensorMap(d->encode, &p.tm_w13, ffn1ExpertWeights, (uint64_t)g.El * 2 * g.I, g.H, 128));
   NA_CHECK(MakeTensorMap(d->encode, &p.tm_act, base + off_act, exp_rows, g.I, 128));
-  NA_CHECK(MakeTensorMap(d->encode, &p.tm_w2, ffn2ExpertWeights, (uint64_t)g.El * g.H, g.I, 128));
-  NA_CHECK(MakeTensorMap(d->encode, &p.tm_gate, gateWeights, (uint64_t)g.E, g.H, std::min(64, g.E)));
+  NA_CHECK(MakeTensorMap(d->encode, &p.tm_w2, ffn2ExpertWeights, (uint64_t)g.El * g.H, g.I, 256));
+  NA_CHECK(MakeTensorMap(d->encode, &p.tm_gate, gateWeights, (uint64_t)g.E, g.H, std::min(128, g.E)));
   p.gate_rows = tokensNum <= 32 * d->grid ? 32 : (tokensNum <= 64 * d->grid ? 64 : 128);
   if (tokensNum > 0)
     NA_CHECK(MakeTensorMap(d->encode, &p.tm_x, tokens, (uint64_t)tokensNum, g.H, std::min(p.gate_rows, tokensNum)));
