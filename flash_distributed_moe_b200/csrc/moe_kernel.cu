@@ -73,6 +73,7 @@ struct __align__(64) SmemCtl {
   uint32_t prof_n;
   uint32_t n_flagged;
   uint32_t pre[16];  // GATED scratch: per-warp totals
+  uint32_t run_round2;  // set by a task body that found this rank's second GATED round due: the group runs it next
   // Copy of the kernel parameters for the task bodies that are compiled as separate functions:
   // there the parameter block is only reachable through a generic pointer, and every access to
   // the constant bank through one costs on the order of a hundred cycles; shared memory does not.
@@ -138,6 +139,16 @@ __device__ __forceinline__ uint32_t atom_add(uint32_t* p, uint32_t v) {
     asm volatile("atom.relaxed.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
   return old;
 }
+template <bool S>
+__device__ __forceinline__ uint32_t atom_exch(uint32_t* p, uint32_t v) {
+  uint32_t old;
+  if (S)
+    asm volatile("atom.acq_rel.sys.global.exch.b32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  else
+    asm volatile("atom.acq_rel.gpu.global.exch.b32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
+
 template <bool S>
 __device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p) {
   uint32_t v;
@@ -322,10 +333,34 @@ __device__ __forceinline__ uint32_t task_word(uint32_t kind, uint32_t e, uint32_
   return kind | (e << 8) | (n << 20);
 }
 
-// Consumer: take a ticket, wait (bounded) until its slot is published or the
-// queue is closed.  Single thread.
+// Consumer (single thread).  A task in the rank's urgent word goes first; otherwise take a
+// ticket and wait (bounded) until its slot is published or the queue is closed.  While it waits
+// the consumer also serves the urgent word; the ticket it holds then stays with it
+// (`has_ticket`) and is waited for on the next call.
+// Urgent word: 0 = none, else 0x80000000 | kind | b << 8.  It carries the GATED tasks, which must
+// not queue up behind the hundreds of PACK tasks they publish.
+__device__ __forceinline__ FdmoeSlot urgent_task(uint32_t word) {
+  FdmoeSlot out;
+  out.seq = 0;
+  out.a = word & 0xffu;
+  out.b = (word >> 8) & 0xffu;
+  out.c = 0;
+  return out;
+}
 template <bool S>
-__device__ __forceinline__ FdmoeSlot queue_pop(const FdmoeParams& p, SmemCtl& sc) {
+__device__ __forceinline__ void push_urgent(const FdmoeParams& p, const FdmoePeer& q, uint32_t kind, uint32_t b) {
+  fence_acqrel<S>();
+  const uint32_t old = atom_exch<S>(&q.ctl->urgent, 0x80000000u | kind | (b << 8));
+  if (old != 0u) {  // (never two at a time by construction; do not lose it if it happens)
+    queue_push<S>(p, q, 1u, [old](uint32_t, uint32_t& a, uint32_t& bb, uint32_t& c) {
+      a = old & 0xffu;
+      bb = (old >> 8) & 0xffu;
+      c = 0;
+    });
+  }
+}
+template <bool S>
+__device__ __forceinline__ FdmoeSlot queue_pop(const FdmoeParams& p, SmemCtl& sc, uint32_t& ticket, bool& has_ticket) {
   const FdmoePeer& me = p.peers[p.rank];
   FdmoeSlot out;
   out.seq = 0;
@@ -333,13 +368,24 @@ __device__ __forceinline__ FdmoeSlot queue_pop(const FdmoeParams& p, SmemCtl& sc
   out.b = 0;
   out.c = 0;
   if (sc.abort) return out;
-  const uint32_t ticket = atomicAdd(&me.ctl->q_tail, 1u);
+  if (!has_ticket) {
+    if (ld_relaxed<S>(&me.ctl->urgent) != 0u) {
+      const uint32_t u = atom_exch<S>(&me.ctl->urgent, 0u);
+      if (u != 0u) return urgent_task(u);
+    }
+    ticket = atomicAdd(&me.ctl->q_tail, 1u);
+    has_ticket = true;
+  }
   FdmoeSlot* s = &me.slots[ticket & (uint32_t)p.queue_mask];
   const uint64_t t0 = ptx::globaltimer_ns();
   uint32_t spins = 0;
   for (;;) {
     if (ld_acquire<S>(&s->seq) == ticket + 1u) break;
     if (ld_relaxed<S>(&me.ctl->closed) != 0u || sc.abort) return out;
+    if (ld_relaxed<S>(&me.ctl->urgent) != 0u) {
+      const uint32_t u = atom_exch<S>(&me.ctl->urgent, 0u);
+      if (u != 0u) return urgent_task(u);
+    }
     if ((++spins & 15u) == 0u) {
       if (ptx::globaltimer_ns() - t0 > p.timeout_ns) {
         raise_error(p, sc, FDMOE_ERR_TIMEOUT_QUEUE, (blockIdx.x << 8));
@@ -348,6 +394,7 @@ __device__ __forceinline__ FdmoeSlot queue_pop(const FdmoeParams& p, SmemCtl& sc
       __nanosleep(100);
     }
   }
+  has_ticket = false;
   out.a = s->a;
   out.b = s->b;
   out.c = s->c;
@@ -370,27 +417,39 @@ __device__ __forceinline__ void maybe_close(const FdmoeParams& p) {
 // The routing of every token of this rank is decided (rows reserved on their
 // owners, send lists complete): tell every rank; whoever completes a rank's
 // count hands it the GATED task, from which its row counts are final.
+// Two things must have happened before rank q's second GATED round may run: every rank has gated,
+// and rank q has laid out its first round (a rank without tokens has none and counts both at once).
+// Whoever brings the count to two hands rank q the task.
+// `sc` non-null: the caller is thread 0 of an epilogue group at the end of a task; if the round
+// falls to its own rank the group runs it right away (flag run_round2) instead of queueing it.
 template <bool S>
-__device__ void gating_finished(const FdmoeParams& p) {
+__device__ __forceinline__ void second_round_ready(const FdmoeParams& p, SmemCtl* sc, int q, uint32_t n) {
+  fence_acqrel<S>();
+  const uint32_t prev = atom_add<S>(&p.peers[q].ctl->round2_rdv, n);
+  if (prev + n == 2u) {
+    if (sc && q == p.rank)
+      sc->run_round2 = 1u;
+    else
+      push_urgent<S>(p, p.peers[q], FDMOE_TASK_GATED, 0u);  // second round
+  }
+}
+
+template <bool S>
+__device__ void gating_finished(const FdmoeParams& p, SmemCtl* sc) {
   for (int q = 0; q < p.world; ++q) {
     fence_acqrel<S>();
     const uint32_t prev = atom_add<S>(&p.peers[q].ctl->ranks_gated, 1u);
-    if (prev == (uint32_t)p.world - 1u) {
-      queue_push<S>(p, p.peers[q], 1u, [](uint32_t, uint32_t& a, uint32_t& b, uint32_t& c) {
-        a = FDMOE_TASK_GATED;
-        b = 0;
-        c = 0;
-      });
-    }
+    // rank q's second round starts when every rank has gated and its own first round is laid out
+    if (prev == (uint32_t)p.world - 1u) second_round_ready<S>(p, sc, q, 1u);
   }
 }
 
 // Counts `n` tokens of this rank as gated; the caller has written their send-list entries.
 template <bool S>
-__device__ __forceinline__ void count_gated(const FdmoeParams& p, uint32_t n) {
+__device__ __forceinline__ void count_gated(const FdmoeParams& p, SmemCtl& sc, uint32_t n) {
   fence_acqrel<S>();
   const uint32_t done = atomicAdd(&p.peers[p.rank].ctl->gated_tokens, n) + n;
-  if (n && done == (uint32_t)p.T) gating_finished<S>(p);
+  if (n && done == (uint32_t)p.T) gating_finished<S>(p, &sc);
 }
 
 // Monotonic unsigned key of a float (larger float <=> larger key; -0 counts as +0).
@@ -639,7 +698,12 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
         c = (2 * i + 1 < nf) ? (uint32_t)t0 + sc.flagged[2 * i + 1] : 0xffffffffu;
       });
     }
-    count_gated<S>(p, (uint32_t)nt - nf);
+    count_gated<S>(p, sc, (uint32_t)nt - nf);
+    // the last GATE tile of this rank: its rows so far (all but those of nearly tied tokens) can be packed
+    const uint32_t tiles = (uint32_t)((p.T + p.gate_rows - 1) / p.gate_rows);
+    fence_acqrel<false>();
+    if (atomicAdd(&p.peers[p.rank].ctl->gate_tiles_done, 1u) + 1u == tiles)
+      push_urgent<false>(p, p.peers[p.rank], FDMOE_TASK_GATED, 1u);  // first round
   }
 }
 
@@ -685,6 +749,44 @@ __device__ __noinline__ bool pack_loads(const FdmoeParams& p, SmemCtl& sc, uint8
   return true;
 }
 
+// All rows of local expert `le` of rank `op` have landed and their number `total` is final: its FFN1
+// tile tasks go onto that rank's queue, m-tile major, so that the tiles of one expert run together and
+// share its weights through L2.  Called by the whole epilogue group; exactly one caller per expert and
+// launch gets to publish (flag `published`).
+template <bool S>
+__device__ __forceinline__ void publish_expert_tiles(const FdmoeParams& p, SmemCtl& sc, int etid, const FdmoePeer& op,
+                                                     uint32_t le, uint32_t total) {
+  const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
+  const uint32_t full = total / 128u, rem = total % 128u, ntask = ((total + 127u) / 128u) * nt1;
+  if (etid == 0) {
+    sc.q_total = 0u;
+    if (atom_exch<S>(&op.published[le], 1u) == 0u) {
+      fence_acqrel<S>();  // the senders' rows (observed through the counter) before the tasks
+      sc.q_t0 = atom_add<S>(&op.ctl->q_head, ntask);
+      sc.q_total = ntask;
+    }
+  }
+  epi_bar();
+  if (sc.q_total) {
+    const uint32_t t0 = sc.q_t0;
+    bool any = false;
+    for (uint32_t idx = etid; idx < ntask; idx += kEpiThreads) {
+      const uint32_t j = idx / nt1, n = idx - j * nt1;
+      FdmoeSlot* sl = &op.slots[(t0 + idx) & (uint32_t)p.queue_mask];
+      sl->a = task_word(FDMOE_TASK_FFN1, le, n);
+      sl->b = j;
+      sl->c = (j < full) ? 128u : rem;
+      any = true;
+    }
+    if (any) {
+      fence_acqrel<S>();
+      for (uint32_t idx = etid; idx < ntask; idx += kEpiThreads)
+        st_relaxed<S>(&op.slots[(t0 + idx) & (uint32_t)p.queue_mask].seq, t0 + idx + 1u);
+    }
+  }
+  epi_bar();  // sc.q_t0 / sc.q_total may be rewritten only after everyone has read them
+}
+
 template <bool S>
 __device__ __noinline__ bool pack_task(const FdmoeParams& p, SmemCtl& sc, uint8_t* stage, uint32_t& stage_it, int etid,
                                        int ewarp, int lane, uint32_t e, uint32_t first, uint32_t count) {
@@ -719,35 +821,16 @@ __device__ __noinline__ bool pack_task(const FdmoeParams& p, SmemCtl& sc, uint8_
   if (etid == 0) {
     fence_acqrel<S>();
     const uint32_t prev = atom_add<S>(&op.landed[le], count);
-    const uint32_t total = ld_relaxed<S>(&op.expert_cnt[le]);  // final: every rank has finished gating
-    sc.flag = (prev + count == total) ? (int)total : 0;
-    if (sc.flag) {
-      const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
-      const uint32_t ntask = ((total + 127u) / 128u) * nt1;
-      fence_acqrel<S>();  // the other senders' rows (observed through the counter) before the tasks
-      sc.q_t0 = atom_add<S>(&op.ctl->q_head, ntask);
-    }
+    // Complete?  The row count of the expert is only final once every rank has gated; before that
+    // the second GATED round of the owner will look at the expert again.  (Sequentially consistent
+    // fences here and there: of this check and that look, at least one sees the other's update.)
+    fence_sc<S>();
+    const uint32_t total = ld_relaxed<S>(&op.expert_cnt[le]);
+    const bool final_cnt = ld_acquire<S>(&op.ctl->ranks_gated) == (uint32_t)p.world;
+    sc.flag = (final_cnt && prev + count == total) ? (int)total : 0;
   }
   epi_bar();
-  if (sc.flag) {
-    const uint32_t total = (uint32_t)sc.flag, nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
-    const uint32_t full = total / 128u, rem = total % 128u, ntask = ((total + 127u) / 128u) * nt1;
-    const uint32_t t0 = sc.q_t0;
-    bool any = false;
-    for (uint32_t idx = etid; idx < ntask; idx += kEpiThreads) {
-      const uint32_t j = idx / nt1, n = idx - j * nt1;
-      FdmoeSlot* sl = &op.slots[(t0 + idx) & (uint32_t)p.queue_mask];
-      sl->a = task_word(FDMOE_TASK_FFN1, (uint32_t)le, n);
-      sl->b = j;
-      sl->c = (j < full) ? 128u : rem;
-      any = true;
-    }
-    if (any) {
-      fence_acqrel<S>();
-      for (uint32_t idx = etid; idx < ntask; idx += kEpiThreads)
-        st_relaxed<S>(&op.slots[(t0 + idx) & (uint32_t)p.queue_mask].seq, t0 + idx + 1u);
-    }
-  }
+  if (sc.flag) publish_expert_tiles<S>(p, sc, etid, op, (uint32_t)le, (uint32_t)sc.flag);
   if (etid == 32) {
     // this piece is done: the next entry of this rank's pack list may go out
     FdmoeCtl* myctl = p.peers[p.rank].ctl;
@@ -837,7 +920,9 @@ __device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uin
         raise_error(p, sc, FDMOE_ERR_ROW_OVERFLOW, (uint32_t)myi);
       } else {
         const size_t rowg = (size_t)le * p.cap_rows + pos;
-        const size_t ent = (size_t)myi * p.send_stride + atomicAdd(&p.send_cnt[myi], 1u);
+        // (entries of re-gated tokens fill the expert's list from the back: the front part is packed
+        // by the first round while these are still being written)
+        const size_t ent = (size_t)myi * p.send_stride + ((uint32_t)p.send_stride - 1u - atomicAdd(&p.send_fix_cnt[myi], 1u));
         p.send_src[ent] = (int32_t)((tok << 4) | (uint32_t)lane);
         p.send_dst[ent] = (int32_t)rowg;
         p.topk_idx[(size_t)tok * K + lane] = myi;
@@ -849,32 +934,36 @@ __device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uin
   }
   epi_bar();
   prof_mark(p, sc, etid, 32);
-  if (etid == 0) count_gated<S>(p, (tok_b != 0xffffffffu) ? 2u : 1u);
+  if (etid == 0) count_gated<S>(p, sc, (tok_b != 0xffffffffu) ? 2u : 1u);
   return true;
 }
 
 // ============================================================ GATED and FFN
-// GATED: every rank has finished gating, so the row counts of this rank's
-// experts and this rank's send lists are final.  Records the number of m-tiles
-// this rank will process (termination), then lays out this rank's PACK tasks
-// (pieces of FDMOE_PACK_ROWS rows of its send lists) in sending order and
-// publishes the first pack_window of them; every PACK task that finishes
-// publishes the next one, so that packing, whose pace is set by memory writes or
-// by NVLink, shares the workers with the FFN1 tiles of the experts that have
-// already landed.  Sending order: step i goes to local expert i / world of rank
-// (rank + 1 + i) % world, so that at every step the ranks send to different
-// owners and the experts of all ranks complete one after the other.
+// GATED lays out this rank's PACK tasks (pieces of FDMOE_PACK_ROWS rows of its send lists), in
+// two rounds.
+// First round, as soon as this rank's GATE tiles are done: the rows of all tokens but the nearly
+// tied ones, in sending order; the first pack_window tasks are published, and every PACK task
+// that finishes publishes the next one, so that packing, whose pace is set by memory writes or by
+// NVLink, shares the workers with the FFN1 tiles of experts that have already landed (and with the
+// GATEFIX tasks that are still re-gating the tied tokens).  Sending order: step i goes to local
+// expert i / world of rank (rank + 1 + i) % world, so that at every step the ranks send to
+// different owners and the experts of all ranks complete one after the other.
+// Second round, once every rank has gated (row counts are final): the rows of the re-gated
+// tokens, the number of m-tiles this rank will process (termination), and a look at this rank's
+// experts for any that landed completely before their count was known to be final.
 template <bool S>
-__device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int etid) {
+__device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int etid, bool first_round) {
   const FdmoePeer& me = p.peers[p.rank];
   const int lane = etid & 31, w = etid >> 5;
-  // (the task was taken from the queue with an acquire load ordered after every rank's reservations)
-  uint32_t ntile = 0, npack = 0, ecnt = 0;
-  const int e_send =
-      (etid < p.E) ? ((p.rank + 1 + etid) % p.world) * p.El + etid / p.world : 0;
-  if (etid < p.El) ntile = (ld_relaxed<S>(&me.expert_cnt[etid]) + 127u) / 128u;
+  // (the task was taken from the queue with an acquire load ordered after the events it stands for)
+  uint32_t ntile = 0, npack = 0, ecnt = 0, lcnt = 0;
+  const int e_send = (etid < p.E) ? ((p.rank + 1 + etid) % p.world) * p.El + etid / p.world : 0;
+  if (!first_round && etid < p.El) {
+    lcnt = ld_relaxed<S>(&me.expert_cnt[etid]);
+    ntile = (lcnt + 127u) / 128u;
+  }
   if (etid < p.E) {
-    ecnt = __ldcg(&p.send_cnt[e_send]);
+    ecnt = __ldcg(first_round ? &p.send_cnt[e_send] : &p.send_fix_cnt[e_send]);
     npack = (ecnt + FDMOE_PACK_ROWS - 1) / FDMOE_PACK_ROWS;
   }
   uint32_t inc_pack = npack, inc_tile = ntile;
@@ -899,18 +988,24 @@ __device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int e
     total += sc.pre[i];
     mt += sc.pre[8 + i];
   }
-  const uint32_t window = min(total, (uint32_t)p.pack_window);
+  // first round: a window of the tasks now, the rest as tasks finish; second round: all at once
+  const uint32_t window = first_round ? min(total, (uint32_t)p.pack_window) : total;
   if (etid == 0) {
     sc.q_t0 = window ? atom_add<false>(&me.ctl->q_head, window) : 0u;
-    st_relaxed<false>(&me.ctl->mtiles_total, mt);
-    st_relaxed<false>(&me.ctl->pack_total, total);
-    st_relaxed<false>(&me.ctl->pack_cursor, window);
+    if (first_round) {
+      st_relaxed<false>(&me.ctl->pack_total, total);
+      st_relaxed<false>(&me.ctl->pack_cursor, window);
+    } else {
+      st_relaxed<false>(&me.ctl->mtiles_total, mt);
+    }
   }
-  // the pack list, in sending order
-  uint4* plist = reinterpret_cast<uint4*>(p.pack_list);
+  // the tasks in sending order: entries [first, first + count) of the expert's send list; the
+  // re-gated tokens' entries sit at the back of the list
+  uint4* plist = reinterpret_cast<uint4*>(p.pack_list) + (first_round ? 0u : (uint32_t)p.pack_list_round2);
   const uint32_t firstslot = off_pack + inc_pack - npack;  // exclusive prefix in sending order
+  const uint32_t ebase = first_round ? 0u : (uint32_t)p.send_stride - ecnt;
   for (uint32_t r = 0; r < npack; ++r)
-    plist[firstslot + r] = make_uint4(task_word(FDMOE_TASK_PACK, (uint32_t)e_send, 0u), r * FDMOE_PACK_ROWS,
+    plist[firstslot + r] = make_uint4(task_word(FDMOE_TASK_PACK, (uint32_t)e_send, 0u), ebase + r * FDMOE_PACK_ROWS,
                                       min((uint32_t)FDMOE_PACK_ROWS, ecnt - r * FDMOE_PACK_ROWS), 0u);
   epi_bar();
   const uint32_t t0 = sc.q_t0;
@@ -927,6 +1022,52 @@ __device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int e
   if (any || etid == 0) fence_acqrel<false>();
   for (uint32_t idx = (uint32_t)etid; idx < window; idx += kEpiThreads)
     st_relaxed<false>(&me.slots[(t0 + idx) & (uint32_t)p.queue_mask].seq, t0 + idx + 1u);
+  epi_bar();
+  if (first_round) {
+    if (etid == 0) second_round_ready<S>(p, &sc, p.rank, 1u);
+    return;
+  }
+  // Experts of this rank whose rows had all landed while their count was not yet known to be final:
+  // nobody has published their tiles.  (Fence: see pack_task.)  Every thread looks at one expert and
+  // claims it; the tasks of all claimed experts are published in one batch.
+  fence_sc<S>();
+  const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
+  const bool cand = etid < p.El && lcnt != 0u && ld_relaxed<S>(&me.landed[etid]) == lcnt &&
+                    atom_exch<S>(&me.published[etid], 1u) == 0u;
+  const uint32_t mytasks = cand ? ((lcnt + 127u) / 128u) * nt1 : 0u;
+  uint32_t inc = mytasks;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const uint32_t a = __shfl_up_sync(0xffffffffu, inc, off);
+    if (lane >= off) inc += a;
+  }
+  if (lane == 31 && w < 4) sc.pre[w] = inc;
+  epi_bar();
+  uint32_t before = 0, all = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (i < w) before += sc.pre[i];
+    all += sc.pre[i];
+  }
+  if (etid == 0 && all) {
+    fence_acqrel<S>();
+    sc.q_t0 = atom_add<false>(&me.ctl->q_head, all);
+  }
+  epi_bar();
+  if (mytasks) {
+    const uint32_t t1 = sc.q_t0 + before + inc - mytasks;
+    const uint32_t full = lcnt / 128u, rem = lcnt % 128u;
+    for (uint32_t idx = 0; idx < mytasks; ++idx) {
+      const uint32_t jt = idx / nt1, n = idx - jt * nt1;
+      FdmoeSlot* sl = &me.slots[(t1 + idx) & (uint32_t)p.queue_mask];
+      sl->a = task_word(FDMOE_TASK_FFN1, (uint32_t)etid, n);
+      sl->b = jt;
+      sl->c = (jt < full) ? 128u : rem;
+    }
+    fence_acqrel<false>();
+    for (uint32_t idx = 0; idx < mytasks; ++idx)
+      st_relaxed<false>(&me.slots[(t1 + idx) & (uint32_t)p.queue_mask].seq, t1 + idx + 1u);
+  }
   epi_bar();
   if (etid == 0) {
     st_release<false>(&me.ctl->gated_done, 1u);
@@ -1075,6 +1216,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       ptx::mbar_init(&sc.done_empty[d], 1);
     }
     sc.abort = 0;
+    sc.run_round2 = 0;
     sc.skip_done = 0;
     sc.flag = 0;
     sc.prof_n = 0;
@@ -1131,7 +1273,10 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
   if (p.mode != 2 && !sc.abort && tid == 0) {
     const uint32_t n_tiles = (p.T > 0 && p.gate_rows > 0) ? (uint32_t)((p.T + p.gate_rows - 1) / p.gate_rows) : 0u;
     if (n_tiles == 0) {
-      if (blockIdx.x == 0) gating_finished<S>(p);
+      if (blockIdx.x == 0) {
+        second_round_ready<S>(p, nullptr, p.rank, 1u);  // no first round to wait for
+        gating_finished<S>(p, nullptr);
+      }
     } else if (blockIdx.x < n_tiles) {
       const uint32_t mine = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
       queue_push<false>(p, me, mine, [](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
@@ -1148,13 +1293,15 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
 
   if (warp == kWarpSched) {
     if (lane == 0) {
+      uint32_t ticket = 0;
+      bool has_ticket = false;
       for (uint32_t it = 0;; ++it) {
         const uint32_t r = it % kRing, ph = (it / kRing) & 1u;
         if (!wait_bar(p, sc, &sc.ring_empty[r], ph ^ 1u, FDMOE_ERR_TIMEOUT_RING)) {
           // The ring may be wedged: hand out EXIT through every slot that is free.
           break;
         }
-        const FdmoeSlot t = queue_pop<S>(p, sc);
+        const FdmoeSlot t = queue_pop<S>(p, sc, ticket, has_ticket);
         sc.ring[r] = t;
         ptx::mbar_arrive(&sc.ring_full[r]);
         const uint32_t kind = t.a & 0xffu;
@@ -1449,7 +1596,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           maybe_close(p);
         }
       } else if (kind == FDMOE_TASK_GATED) {
-        gated_task<S>(sc.params, sc, etid);
+        gated_task<S>(sc.params, sc, etid, j == 1u);
       } else if (kind == FDMOE_TASK_TESTA || kind == FDMOE_TASK_TESTB) {
         // task-system self test: two dependent stages over a 256-element chunk
         int* ptr = p.test_buf + (size_t)j * kEpiThreads + etid;
@@ -1469,6 +1616,16 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         }
       } else {
         if (etid == 0) raise_error(p, sc, FDMOE_ERR_BAD_TASK, t.a);
+      }
+      if (kind == FDMOE_TASK_GATE || kind == FDMOE_TASK_GATEFIX || kind == FDMOE_TASK_GATED) {
+        // the task may have found this rank's second GATED round due: run it here and now
+        epi_bar();
+        const bool r2 = sc.run_round2 != 0u;
+        epi_bar();
+        if (r2) {
+          if (etid == 0) sc.run_round2 = 0u;
+          gated_task<S>(sc.params, sc, etid, false);
+        }
       }
       if (p.mode == 2) {
         epi_bar();
