@@ -35,7 +35,7 @@ inline uint32_t NextPow2(uint64_t v) {
 // ranks, so a peer's regions are found from its base pointer alone.
 struct ArenaLayout {
   size_t ctl = 0;
-  size_t expert_cnt = 0, landed = 0, published = 0, send_cnt = 0, send_fix_cnt = 0, ffn1_done = 0, ffn2_done = 0;
+  size_t expert_cnt = 0, landed = 0, published = 0, send_cnt = 0, ffn1_done = 0, ffn2_done = 0;
   size_t zero_begin = 0, zero_end = 0;  // per-launch reset range
   size_t slots = 0, meta = 0, ystage = 0, packed = 0;
   size_t total = 0;
@@ -67,12 +67,8 @@ inline uint32_t QueueCapacity(const Geometry& g, int grid) {
 
 // A rank's pack list: one 16-byte entry per PACK task; an expert's rows come in pieces of
 // FDMOE_PACK_ROWS with one ragged piece per expert.
-// The two rounds (rows of the GATE tiles; rows of re-gated tokens) have a region each.
-inline size_t PackListRoundEntries(const Geometry& g, int max_tokens_local) {
-  return (size_t)std::max(max_tokens_local, 1) * g.K / FDMOE_PACK_ROWS + g.E + 8;
-}
 inline size_t PackListBytes(const Geometry& g, int max_tokens_local) {
-  return 2 * PackListRoundEntries(g, max_tokens_local) * 16;
+  return ((size_t)std::max(max_tokens_local, 1) * g.K / FDMOE_PACK_ROWS + g.E + 8) * 16;
 }
 
 inline ArenaLayout MakeLayout(const Geometry& g) {
@@ -88,8 +84,6 @@ inline ArenaLayout MakeLayout(const Geometry& g) {
   L.published = off;
   off += AlignUp((size_t)g.El * 4, 128);
   L.send_cnt = off;
-  off += AlignUp((size_t)g.E * 4, 128);
-  L.send_fix_cnt = off;
   off += AlignUp((size_t)g.E * 4, 128);
   L.ffn1_done = off;
   off += AlignUp((size_t)g.El * g.MT * 4, 128);

@@ -339,14 +339,12 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   params_.send_src = send_src_;
   params_.send_dst = send_dst_;
   params_.pack_list = pack_list_;
-  params_.pack_list_round2 = (int32_t)PackListRoundEntries(g_, maxTokens);
   // PACK tasks outstanding at a time.  On one GPU packing is bound by memory writes and is fastest with
   // every worker on it at once; across GPUs a window leaves workers for the FFN1 tiles of landed
   // experts while rows are still crossing NVLink.
   params_.pack_window = std::max(1, EnvInt("FLASHMOE_PACK_WINDOW", world > 1 ? 128 : (1 << 30)));
   params_.send_stride = (int32_t)AlignUp((size_t)std::max(maxTokens, 1), 4);
   params_.send_cnt = reinterpret_cast<uint32_t*>(arena_ + layout_.send_cnt);
-  params_.send_fix_cnt = reinterpret_cast<uint32_t*>(arena_ + layout_.send_fix_cnt);
   params_.ffn1_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn1_done);
   params_.ffn2_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn2_done);
   params_.status_host = status_dev_;

@@ -100,6 +100,7 @@ struct __align__(64) SmemCtl {
       // GATEFIX task scratch: two token rows and their exact logits
       uint4 xrow[2][FDMOE_MAX_HIDDEN / 8];
       float exact[2][128];
+      uint2 fix_dst[2][FDMOE_MAX_TOPK];         // {expert, row in the owner's buffers} of each slot, or {~0, 0}
     };
     // FFN epilogues: per-warp staging of a 32-row x 64-byte chunk (80-byte pitch
     // keeps the 16-byte accesses of a quarter warp on distinct banks)
@@ -916,15 +917,12 @@ __device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uin
       const float w = ex / sum;
       const int owner = myi / p.El, le = myi - owner * p.El;
       const uint32_t pos = atom_add<S>(&p.peers[owner].expert_cnt[le], 1u);
+      sc.fix_dst[half][lane] = make_uint2(0xffffffffu, 0u);
       if (pos >= (uint32_t)p.cap_rows) {
         raise_error(p, sc, FDMOE_ERR_ROW_OVERFLOW, (uint32_t)myi);
       } else {
         const size_t rowg = (size_t)le * p.cap_rows + pos;
-        // (entries of re-gated tokens fill the expert's list from the back: the front part is packed
-        // by the first round while these are still being written)
-        const size_t ent = (size_t)myi * p.send_stride + ((uint32_t)p.send_stride - 1u - atomicAdd(&p.send_fix_cnt[myi], 1u));
-        p.send_src[ent] = (int32_t)((tok << 4) | (uint32_t)lane);
-        p.send_dst[ent] = (int32_t)rowg;
+        sc.fix_dst[half][lane] = make_uint2((uint32_t)myi, (uint32_t)rowg);  // this task sends the row itself (below)
         p.topk_idx[(size_t)tok * K + lane] = myi;
         p.topk_w[(size_t)tok * K + lane] = w;
         *reinterpret_cast<uint4*>(&p.peers[owner].meta[rowg]) =
@@ -934,23 +932,47 @@ __device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uin
   }
   epi_bar();
   prof_mark(p, sc, etid, 32);
+  // The token row (still in shared memory) goes to its K rows in the owners' expert buffers: these few
+  // rows do not pass through PACK tasks.  Their landing counts as gated only below, so no expert can be
+  // found complete with its count believed final before these rows are there; the second GATED round
+  // looks at the experts they completed.
+  if (live) {
+    for (int k = 0; k < K; ++k) {
+      const uint2 d = sc.fix_dst[half][k];
+      if (d.x == 0xffffffffu) continue;
+      const int owner = (int)d.x / p.El;
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.peers[owner].packed) + (size_t)d.y * H);
+      for (int v = e; v < H / 8; v += 128) dst[v] = sc.xrow[half][v];
+    }
+    fence_acqrel<S>();
+    ptx::fence_proxy_async();  // packed rows are read by TMA
+  }
+  epi_bar();
+  if (live && e < K) {
+    const uint2 d = sc.fix_dst[half][e];
+    if (d.x != 0xffffffffu) {
+      const int owner = (int)d.x / p.El, le = (int)d.x - owner * p.El;
+      fence_acqrel<S>();
+      atom_add<S>(&p.peers[owner].landed[le], 1u);
+    }
+  }
+  epi_bar();
   if (etid == 0) count_gated<S>(p, sc, (tok_b != 0xffffffffu) ? 2u : 1u);
   return true;
 }
 
 // ============================================================ GATED and FFN
-// GATED lays out this rank's PACK tasks (pieces of FDMOE_PACK_ROWS rows of its send lists), in
-// two rounds.
-// First round, as soon as this rank's GATE tiles are done: the rows of all tokens but the nearly
-// tied ones, in sending order; the first pack_window tasks are published, and every PACK task
-// that finishes publishes the next one, so that packing, whose pace is set by memory writes or by
-// NVLink, shares the workers with the FFN1 tiles of experts that have already landed (and with the
-// GATEFIX tasks that are still re-gating the tied tokens).  Sending order: step i goes to local
+// GATED, first round, as soon as this rank's GATE tiles are done: lays out this rank's PACK tasks
+// (pieces of FDMOE_PACK_ROWS rows of its send lists: the rows of all tokens but the nearly tied
+// ones, which their GATEFIX tasks send themselves) in sending order and publishes the first
+// pack_window of them; every PACK task that finishes publishes the next one, so that packing,
+// whose pace is set by memory writes or by NVLink, shares the workers with the GATEFIX tasks and
+// with the FFN1 tiles of experts that have already landed.  Sending order: step i goes to local
 // expert i / world of rank (rank + 1 + i) % world, so that at every step the ranks send to
 // different owners and the experts of all ranks complete one after the other.
-// Second round, once every rank has gated (row counts are final): the rows of the re-gated
-// tokens, the number of m-tiles this rank will process (termination), and a look at this rank's
-// experts for any that landed completely before their count was known to be final.
+// Second round, once every rank has gated (row counts are final): the number of m-tiles this
+// rank will process (termination), and a look at this rank's experts for any that landed
+// completely before their count was known to be final.
 template <bool S>
 __device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int etid, bool first_round) {
   const FdmoePeer& me = p.peers[p.rank];
@@ -962,8 +984,8 @@ __device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int e
     lcnt = ld_relaxed<S>(&me.expert_cnt[etid]);
     ntile = (lcnt + 127u) / 128u;
   }
-  if (etid < p.E) {
-    ecnt = __ldcg(first_round ? &p.send_cnt[e_send] : &p.send_fix_cnt[e_send]);
+  if (first_round && etid < p.E) {
+    ecnt = __ldcg(&p.send_cnt[e_send]);
     npack = (ecnt + FDMOE_PACK_ROWS - 1) / FDMOE_PACK_ROWS;
   }
   uint32_t inc_pack = npack, inc_tile = ntile;
@@ -988,45 +1010,39 @@ __device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int e
     total += sc.pre[i];
     mt += sc.pre[8 + i];
   }
-  // first round: a window of the tasks now, the rest as tasks finish; second round: all at once
-  const uint32_t window = first_round ? min(total, (uint32_t)p.pack_window) : total;
-  if (etid == 0) {
-    sc.q_t0 = window ? atom_add<false>(&me.ctl->q_head, window) : 0u;
-    if (first_round) {
+  if (first_round) {
+    const uint32_t window = min(total, (uint32_t)p.pack_window);
+    if (etid == 0) {
+      sc.q_t0 = window ? atom_add<false>(&me.ctl->q_head, window) : 0u;
       st_relaxed<false>(&me.ctl->pack_total, total);
       st_relaxed<false>(&me.ctl->pack_cursor, window);
-    } else {
-      st_relaxed<false>(&me.ctl->mtiles_total, mt);
     }
-  }
-  // the tasks in sending order: entries [first, first + count) of the expert's send list; the
-  // re-gated tokens' entries sit at the back of the list
-  uint4* plist = reinterpret_cast<uint4*>(p.pack_list) + (first_round ? 0u : (uint32_t)p.pack_list_round2);
-  const uint32_t firstslot = off_pack + inc_pack - npack;  // exclusive prefix in sending order
-  const uint32_t ebase = first_round ? 0u : (uint32_t)p.send_stride - ecnt;
-  for (uint32_t r = 0; r < npack; ++r)
-    plist[firstslot + r] = make_uint4(task_word(FDMOE_TASK_PACK, (uint32_t)e_send, 0u), ebase + r * FDMOE_PACK_ROWS,
-                                      min((uint32_t)FDMOE_PACK_ROWS, ecnt - r * FDMOE_PACK_ROWS), 0u);
-  epi_bar();
-  const uint32_t t0 = sc.q_t0;
-  bool any = false;
-  for (uint32_t idx = (uint32_t)etid; idx < window; idx += kEpiThreads) {
-    const uint4 t = ld_cg_u4(&plist[idx]);
-    FdmoeSlot* sl = &me.slots[(t0 + idx) & (uint32_t)p.queue_mask];
-    sl->a = t.x;
-    sl->b = t.y;
-    sl->c = t.z;
-    any = true;
-  }
-  // one fence orders every payload (and the list, the cursor and the totals) before every sequence word below
-  if (any || etid == 0) fence_acqrel<false>();
-  for (uint32_t idx = (uint32_t)etid; idx < window; idx += kEpiThreads)
-    st_relaxed<false>(&me.slots[(t0 + idx) & (uint32_t)p.queue_mask].seq, t0 + idx + 1u);
-  epi_bar();
-  if (first_round) {
+    // the tasks in sending order: entries [first, first + count) of the expert's send list
+    uint4* plist = reinterpret_cast<uint4*>(p.pack_list);
+    const uint32_t firstslot = off_pack + inc_pack - npack;  // exclusive prefix in sending order
+    for (uint32_t r = 0; r < npack; ++r)
+      plist[firstslot + r] = make_uint4(task_word(FDMOE_TASK_PACK, (uint32_t)e_send, 0u), r * FDMOE_PACK_ROWS,
+                                        min((uint32_t)FDMOE_PACK_ROWS, ecnt - r * FDMOE_PACK_ROWS), 0u);
+    epi_bar();
+    const uint32_t t0 = sc.q_t0;
+    bool any = false;
+    for (uint32_t idx = (uint32_t)etid; idx < window; idx += kEpiThreads) {
+      const uint4 t = ld_cg_u4(&plist[idx]);
+      FdmoeSlot* sl = &me.slots[(t0 + idx) & (uint32_t)p.queue_mask];
+      sl->a = t.x;
+      sl->b = t.y;
+      sl->c = t.z;
+      any = true;
+    }
+    // one fence orders every payload (and the list, the cursor and the total) before every sequence word below
+    if (any || etid == 0) fence_acqrel<false>();
+    for (uint32_t idx = (uint32_t)etid; idx < window; idx += kEpiThreads)
+      st_relaxed<false>(&me.slots[(t0 + idx) & (uint32_t)p.queue_mask].seq, t0 + idx + 1u);
+    epi_bar();
     if (etid == 0) second_round_ready<S>(p, &sc, p.rank, 1u);
     return;
   }
+  if (etid == 0) st_relaxed<false>(&me.ctl->mtiles_total, mt);
   // Experts of this rank whose rows had all landed while their count was not yet known to be final:
   // nobody has published their tiles.  (Fence: see pack_task.)  Every thread looks at one expert and
   // claims it; the tasks of all claimed experts are published in one batch.

@@ -92,7 +92,7 @@ typedef struct {
   uint32_t tokens_combined;
   uint32_t tokens_launch;    // tokens of this rank this launch (written at kernel start)
   uint32_t executed;         // tasks finished (used only with expected_static)
-  uint32_t pack_total;       // PACK tasks of this rank's first round (entries of its pack list)
+  uint32_t pack_total;       // PACK tasks of this rank this launch (entries of its pack list)
   uint32_t pack_cursor;      // next entry of the pack list to publish
   uint32_t gate_tiles_done;  // GATE tiles of this rank that have finished
   uint32_t round2_rdv;       // 2 when both this rank's first round is laid out and every rank has gated
@@ -152,7 +152,6 @@ typedef struct {
   float* topk_w;        // [max_tokens, K]
   // this rank's send lists, one per (global) expert: entry i of expert e is at [e * send_stride + i]
   uint32_t* send_cnt;   // [E] entries per expert (zeroed per launch)
-  uint32_t* send_fix_cnt;  // [E] entries of re-gated (GATEFIX) tokens, which fill a list from its back (zeroed per launch)
   int32_t* send_src;    // token << 4 | slot
   int32_t* send_dst;    // row in the owner's expert buffers
   int32_t send_stride;  // = max tokens of this rank (an expert gets at most one row per token)
@@ -160,7 +159,6 @@ typedef struct {
   // are outstanding at a time (every finished PACK task publishes the next entry)
   uint32_t* pack_list;
   int32_t pack_window;
-  int32_t pack_list_round2;  // first entry of the second round's tasks in pack_list
   uint32_t* ffn1_done;  // [El * MT]
   uint32_t* ffn2_done;  // [El * MT]
   uint32_t* status_host;  // mapped pinned word: first error code, readable without a sync

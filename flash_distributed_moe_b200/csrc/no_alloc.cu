@@ -200,11 +200,9 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   p.topk_idx = reinterpret_cast<int32_t*>(base + off_idx);
   p.topk_w = reinterpret_cast<float*>(base + off_w);
   p.send_cnt = reinterpret_cast<uint32_t*>(base + L.send_cnt);
-  p.send_fix_cnt = reinterpret_cast<uint32_t*>(base + L.send_fix_cnt);
   p.send_src = reinterpret_cast<int32_t*>(base + off_src);
   p.send_dst = reinterpret_cast<int32_t*>(base + off_dst);
   p.pack_list = reinterpret_cast<uint32_t*>(base + off_plist);
-  p.pack_list_round2 = (int32_t)PackListRoundEntries(g, g.max_tokens_max);
   p.pack_window = 1 << 30;
   p.send_stride = (int32_t)AlignUp((size_t)g.max_tokens_max, 4);
   p.ffn1_done = reinterpret_cast<uint32_t*>(base + L.ffn1_done);
