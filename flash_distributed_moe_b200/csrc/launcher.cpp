@@ -343,6 +343,9 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   // every worker on it at once; across GPUs a window leaves workers for the FFN1 tiles of landed
   // experts while rows are still crossing NVLink.
   params_.pack_window = std::max(1, EnvInt("FLASHMOE_PACK_WINDOW", world > 1 ? 128 : (1 << 30)));
+  // Packing starts while nearly tied tokens are still re-gated (measured faster on one and on two GPUs;
+  // 0 holds it back until every rank has gated).
+  params_.pack_early = EnvInt("FLASHMOE_PACK_EARLY", 1) != 0;
   params_.send_stride = (int32_t)AlignUp((size_t)std::max(maxTokens, 1), 4);
   params_.send_cnt = reinterpret_cast<uint32_t*>(arena_ + layout_.send_cnt);
   params_.ffn1_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn1_done);

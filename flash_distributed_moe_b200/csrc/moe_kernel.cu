@@ -703,8 +703,12 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
     // the last GATE tile of this rank: its rows so far (all but those of nearly tied tokens) can be packed
     const uint32_t tiles = (uint32_t)((p.T + p.gate_rows - 1) / p.gate_rows);
     fence_acqrel<false>();
-    if (atomicAdd(&p.peers[p.rank].ctl->gate_tiles_done, 1u) + 1u == tiles)
-      push_urgent<false>(p, p.peers[p.rank], FDMOE_TASK_GATED, 1u);  // first round
+    if (atomicAdd(&p.peers[p.rank].ctl->gate_tiles_done, 1u) + 1u == tiles) {
+      if (p.pack_early)
+        push_urgent<false>(p, p.peers[p.rank], FDMOE_TASK_GATED, 1u);  // first round now
+      else
+        second_round_ready<S>(p, &sc, p.rank, 1u);  // both rounds once every rank has gated
+    }
   }
 }
 
@@ -1039,7 +1043,7 @@ __device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int e
     for (uint32_t idx = (uint32_t)etid; idx < window; idx += kEpiThreads)
       st_relaxed<false>(&me.slots[(t0 + idx) & (uint32_t)p.queue_mask].seq, t0 + idx + 1u);
     epi_bar();
-    if (etid == 0) second_round_ready<S>(p, &sc, p.rank, 1u);
+    if (etid == 0 && p.pack_early) second_round_ready<S>(p, &sc, p.rank, 1u);
     return;
   }
   if (etid == 0) st_relaxed<false>(&me.ctl->mtiles_total, mt);
@@ -1612,6 +1616,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           maybe_close(p);
         }
       } else if (kind == FDMOE_TASK_GATED) {
+        if (j == 0u && !p.pack_early) gated_task<S>(sc.params, sc, etid, true);  // packing was held back until now
         gated_task<S>(sc.params, sc, etid, j == 1u);
       } else if (kind == FDMOE_TASK_TESTA || kind == FDMOE_TASK_TESTB) {
         // task-system self test: two dependent stages over a 256-element chunk
@@ -1640,6 +1645,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         epi_bar();
         if (r2) {
           if (etid == 0) sc.run_round2 = 0u;
+          if (!p.pack_early) gated_task<S>(sc.params, sc, etid, true);
           gated_task<S>(sc.params, sc, etid, false);
         }
       }

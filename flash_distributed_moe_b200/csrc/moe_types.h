@@ -159,6 +159,7 @@ typedef struct {
   // are outstanding at a time (every finished PACK task publishes the next entry)
   uint32_t* pack_list;
   int32_t pack_window;
+  int32_t pack_early;   // 1: packing starts when this rank's GATE tiles are done; 0: when every rank has gated
   uint32_t* ffn1_done;  // [El * MT]
   uint32_t* ffn2_done;  // [El * MT]
   uint32_t* status_host;  // mapped pinned word: first error code, readable without a sync

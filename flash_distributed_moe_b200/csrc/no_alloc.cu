@@ -204,6 +204,7 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   p.send_dst = reinterpret_cast<int32_t*>(base + off_dst);
   p.pack_list = reinterpret_cast<uint32_t*>(base + off_plist);
   p.pack_window = 1 << 30;
+  p.pack_early = 1;
   p.send_stride = (int32_t)AlignUp((size_t)g.max_tokens_max, 4);
   p.ffn1_done = reinterpret_cast<uint32_t*>(base + L.ffn1_done);
   p.ffn2_done = reinterpret_cast<uint32_t*>(base + L.ffn2_done);
