@@ -1577,10 +1577,9 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         for (int tk = t_begin; tk < t_end && ok; ++tk) {
           for (int c0 = 0; c0 < p.H; c0 += kCombineCols, ++stage_it) {
             const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
-            ok = epi_vote_all(wait_bar(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE));
-            if (!ok) break;
+            const bool landed = wait_bar(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE);
             const int nvec = min(kCombineCols, p.H - c0) / 8;
-            if (etid < nvec) {
+            if (landed && etid < nvec) {
               const uint4* sm = reinterpret_cast<const uint4*>(stage + s * kStageBytes) + etid;
               float acc[8];
 #pragma unroll
@@ -1601,7 +1600,8 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
               o.w = pack_bf16(acc[6], acc[7]);
               *reinterpret_cast<uint4*>(outp + (size_t)tk * p.H + c0 + etid * 8) = o;
             }
-            epi_bar();  // every thread has read the stage
+            ok = epi_vote_all(landed);  // every thread has read the stage (or the group gives up together)
+            if (!ok) break;
             if (etid == 0) ptx::mbar_arrive(&sc.empty_bar[s]);
           }
         }
@@ -1716,11 +1716,15 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           uint32_t cnt[FDMOE_MAX_WORLD];
 #pragma unroll
           for (int w = 0; w < FDMOE_MAX_WORLD; ++w) cnt[w] = 0u;
-          for (uint32_t r = lane; r < rows; r += 32) {
-            const uint4 mraw = ld_cg_u4(&me.meta[(size_t)e * p.cap_rows + (size_t)j * 128 + r]);
-            const int home = (int)mraw.y >> 8;
+          if (p.world == 1) {
+            if (lane == 0) cnt[0] = rows;  // every row is this rank's own
+          } else {
+            for (uint32_t r = lane; r < rows; r += 32) {
+              const uint4 mraw = ld_cg_u4(&me.meta[(size_t)e * p.cap_rows + (size_t)j * 128 + r]);
+              const int home = (int)mraw.y >> 8;
 #pragma unroll
-            for (int w = 0; w < FDMOE_MAX_WORLD; ++w) cnt[w] += (home == w) ? 1u : 0u;
+              for (int w = 0; w < FDMOE_MAX_WORLD; ++w) cnt[w] += (home == w) ? 1u : 0u;
+            }
           }
           uint32_t mine = 0u;
 #pragma unroll
