@@ -718,10 +718,9 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
 // the TMA warp brings up to pack_rows_per_stage() token rows into a pipeline
 // stage, the lanes of the first epilogue warp send one row each from there into
 // the owner's expert buffer (local, or a peer's over NVLink).  The sender whose
-// rows complete the expert (all ranks have finished gating before any PACK task
-// exists, so the expert's row count is final) publishes all its FFN1 tile tasks
-// on the owner's queue, m-tile major, so that the tiles of one expert run
-// together and share its weights through L2.
+// rows complete the expert while its row count is known to be final (every rank
+// has gated) publishes the expert's FFN1 tile tasks on the owner's queue; an
+// expert that completes earlier is left to the owner's second GATED round.
 __device__ __forceinline__ uint32_t pack_rows_per_stage(int H) {
   return min(16u, (uint32_t)kStageBytes / ((uint32_t)H * 2u));
 }
