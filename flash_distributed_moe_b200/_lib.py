@@ -16,7 +16,7 @@ EXPORTED_SYMBOLS = [
     "GetDistributedUniqueId", "CreateLauncher", "CreateLauncherEx", "DestroyLauncher",
     "FlashMoeGetUniqueId", "FlashMoeCreate", "FlashMoeLaunch", "FlashMoeLaunchHost",
     "FlashMoeDestroy", "FlashMoeGetLastStatus", "FlashMoeDebugRead", "FlashMoeTestTaskSystem",
-    "FlashMoeTestQueueGemm", "FlashMoeTestPairGemm", "FlashMoeErrorString", "FlashMoeLaunchNoAlloc",
+    "FlashMoeTestQueueGemm", "FlashMoeErrorString", "FlashMoeLaunchNoAlloc",
 ]
 
 
@@ -50,14 +50,13 @@ def lib() -> C.CDLL:
     L.FlashMoeDebugRead.argtypes = [vp, C.c_int, vp, C.c_size_t, C.c_size_t]
     L.FlashMoeTestTaskSystem.argtypes = [vp, vp, C.c_int, vp]
     L.FlashMoeTestQueueGemm.argtypes = [vp, C.POINTER(C.c_uint32), vp, vp, vp]
-    L.FlashMoeTestPairGemm.argtypes = [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_uint), vp]
     L.FlashMoeLaunchNoAlloc.argtypes = [vp, vp, vp, vp, vp, C.c_int, C.POINTER(FlashMoeConfig), vp]
     L.FlashMoeLaunchNoAlloc.restype = C.c_int
     L.FlashMoeErrorString.argtypes = [C.c_int]
     L.FlashMoeErrorString.restype = C.c_char_p
     for fn in ("FlashMoeGetUniqueId", "FlashMoeCreate", "FlashMoeLaunch", "FlashMoeLaunchHost",
                "FlashMoeDestroy", "FlashMoeGetLastStatus", "FlashMoeDebugRead",
-               "FlashMoeTestTaskSystem", "FlashMoeTestQueueGemm", "FlashMoeTestPairGemm"):
+               "FlashMoeTestTaskSystem", "FlashMoeTestQueueGemm"):
         getattr(L, fn).restype = C.c_int
     _lib = L
     return L

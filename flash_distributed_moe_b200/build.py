@@ -14,7 +14,7 @@ import sys
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB = os.path.join(_HERE, "libflashMoe.so")
-SOURCES = ["moe_kernel.cu", "no_alloc.cu", "pair_gemm.cu", "launcher.cpp", "bootstrap.cpp"]
+SOURCES = ["moe_kernel.cu", "no_alloc.cu", "launcher.cpp", "bootstrap.cpp"]
 HEADERS = ["moe_types.h", "ptx.cuh", "bootstrap.h", "host_layout.h", "lib.version",
            os.path.join("..", "..", "include", "iMoeKernelLauncher.h"),
            os.path.join("..", "..", "include", "flashmoe_c.h")]

@@ -35,9 +35,10 @@ inline uint32_t NextPow2(uint64_t v) {
 // ranks, so a peer's regions are found from its base pointer alone.
 struct ArenaLayout {
   size_t ctl = 0;
-  size_t expert_cnt = 0, landed = 0, published = 0, send_cnt = 0, ffn1_done = 0, ffn2_done = 0;
+  size_t expert_cnt = 0, landed = 0, grp_cnt = 0, ffn1_done = 0, ffn2_done = 0;
   size_t zero_begin = 0, zero_end = 0;  // per-launch reset range
-  size_t slots = 0, meta = 0, ystage = 0, packed = 0;
+  size_t slots[3] = {0, 0, 0};
+  size_t meta = 0, ystage = 0, packed = 0;
   size_t total = 0;
 };
 
@@ -46,29 +47,26 @@ struct Geometry {
   int max_tokens_local = 0;  // this rank
   int max_tokens_max = 0;    // largest over ranks (sizes token-indexed regions)
   int64_t max_tokens_sum = 0;  // all ranks (sizes expert buffers)
-  int cap_rows = 0, MT = 0, combine_group = 16;  // combine_group: most tokens per COMBINE task
+  int cap_rows = 0, MT = 0, combine_group = 8;  // combine_group: tokens per COMBINE task
   uint32_t queue_cap = 0;
 };
 
-// Slots of a rank's task queue: at least every task one launch can publish there, so that a
-// slot is never reused within a launch.  Tile tasks of the rank's experts, COMBINE tasks (at
-// most max_tokens / combine_group + one wave of `grid`), GATED, this rank's GATE tasks (>= 32
-// tokens each), PACK pieces (FDMOE_PACK_ROWS rows, one ragged piece per expert) and GATEFIX
-// tasks (two tokens each, every token in the worst case), plus EXIT tickets of every worker.
+// Slots of any task queue of a rank: at least every task one launch can publish there, so
+// that a slot is never reused within a launch.  Tile tasks of the rank's experts (FFN1 in one
+// queue, FFN2 in the other), COMBINE tasks (one per group of combine_group tokens), GATEFIX
+// tasks (two tokens each, every token in the worst case), the GATED round, and DISPATCH tasks (one
+// per GATE tile of at least 32 tokens).
 inline uint32_t QueueCapacity(const Geometry& g, int grid) {
   const uint64_t rows_max = std::min<uint64_t>((uint64_t)g.max_tokens_sum * g.K, (uint64_t)g.El * g.cap_rows);
   const uint64_t mtiles = rows_max / FDMOE_TILE_M + g.El;
-  const uint64_t tasks = mtiles * (g.I / FDMOE_TILE_N1 + g.H / FDMOE_TILE_N2) +
-                         (uint64_t)g.max_tokens_max / std::max(1, g.combine_group) + grid + 64 +
-                         (uint64_t)g.max_tokens_max / 32 + (uint64_t)g.max_tokens_max * g.K / FDMOE_PACK_ROWS + g.E +
-                         (uint64_t)g.max_tokens_max / 2 + 1024;
-  return NextPow2(tasks + 4ull * grid + 1024);
+  const uint64_t tiles = mtiles * (uint64_t)std::max(g.I / FDMOE_TILE_N1, g.H / FDMOE_TILE_N2);
+  const uint64_t tasks = tiles + (uint64_t)g.max_tokens_max / std::max(1, g.combine_group) +
+                         (uint64_t)g.max_tokens_max / 2 + (uint64_t)grid + 1024;
+  return NextPow2(tasks + 1024);
 }
 
-// A rank's pack list: one 16-byte entry per PACK task; an expert's rows come in pieces of
-// FDMOE_PACK_ROWS with one ragged piece per expert.
-inline size_t PackListBytes(const Geometry& g, int max_tokens_local) {
-  return ((size_t)std::max(max_tokens_local, 1) * g.K / FDMOE_PACK_ROWS + g.E + 8) * 16;
+inline size_t CombineGroups(const Geometry& g) {
+  return (size_t)g.max_tokens_max / std::max(1, g.combine_group) + 2;
 }
 
 inline ArenaLayout MakeLayout(const Geometry& g) {
@@ -80,18 +78,18 @@ inline ArenaLayout MakeLayout(const Geometry& g) {
   L.expert_cnt = off;
   off += AlignUp((size_t)g.El * 4, 128);
   L.landed = off;
-  off += AlignUp((size_t)g.El * 4, 128);
-  L.published = off;
-  off += AlignUp((size_t)g.El * 4, 128);
-  L.send_cnt = off;
-  off += AlignUp((size_t)g.E * 4, 128);
+  off += AlignUp((size_t)g.El * g.MT * 4, 128);
+  L.grp_cnt = off;
+  off += AlignUp(CombineGroups(g) * 4, 128);
   L.ffn1_done = off;
   off += AlignUp((size_t)g.El * g.MT * 4, 128);
   L.ffn2_done = off;
   off += AlignUp((size_t)g.El * g.MT * 4, 128);
   L.zero_end = off;
-  L.slots = off;
-  off += AlignUp((size_t)g.queue_cap * sizeof(FdmoeSlot), 1024);
+  for (int q = 0; q < 3; ++q) {
+    L.slots[q] = off;
+    off += AlignUp((size_t)g.queue_cap * sizeof(FdmoeSlot), 1024);
+  }
   L.meta = off;
   off += AlignUp((size_t)g.El * g.cap_rows * sizeof(FdmoeRowMeta), 1024);
   L.ystage = off;

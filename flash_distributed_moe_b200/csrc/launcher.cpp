@@ -91,9 +91,7 @@ class MoeKernelLauncher final : public moe::IMoeKernelLauncher {
   void* act_ = nullptr;
   int32_t* topk_idx_ = nullptr;
   float* topk_w_ = nullptr;
-  int32_t* send_src_ = nullptr;  // this rank's send lists [E][maxTokens]
-  int32_t* send_dst_ = nullptr;
-  uint32_t* pack_list_ = nullptr;  // this rank's PACK tasks of a launch in sending order
+  uint8_t* tok_flag_ = nullptr;  // per token: routed by a GATEFIX task
   uint32_t* status_host_ = nullptr;
   uint32_t* status_dev_ = nullptr;
   // fp32 I/O mode: bf16 copies of the weights and token staging
@@ -126,7 +124,7 @@ void MoeKernelLauncher::FreeAll() {
   for (int r = 0; r < (int)peer_bases_.size(); ++r)
     if (r != rank_ && peer_bases_[r]) cudaIpcCloseMemHandle(peer_bases_[r]);
   peer_bases_.clear();
-  void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, send_src_, send_dst_, pack_list_, gate_bf16_, w13_bf16_, w2_bf16_,
+  void* ptrs[] = {arena_, act_, topk_idx_, topk_w_, tok_flag_, gate_bf16_, w13_bf16_, w2_bf16_,
                   tok_bf16_, out_bf16_, pipe_.in[0], pipe_.in[1], pipe_.out[0], pipe_.out[1], prof_, debug_logits_,
                   stuck_};
   for (void* p : ptrs)
@@ -135,8 +133,7 @@ void MoeKernelLauncher::FreeAll() {
   act_ = nullptr;
   topk_idx_ = nullptr;
   topk_w_ = nullptr;
-  send_src_ = send_dst_ = nullptr;
-  pack_list_ = nullptr;
+  tok_flag_ = nullptr;
   gate_bf16_ = w13_bf16_ = w2_bf16_ = tok_bf16_ = out_bf16_ = nullptr;
   pipe_.in[0] = pipe_.in[1] = pipe_.out[0] = pipe_.out[1] = nullptr;
   prof_ = nullptr;
@@ -228,7 +225,12 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   }
   g_.cap_rows = (int)AlignUp((size_t)std::max<int64_t>(g_.max_tokens_sum, 1), FDMOE_TILE_M);
   g_.MT = g_.cap_rows / FDMOE_TILE_M;
-  g_.combine_group = std::max(1, EnvInt("FLASHMOE_COMBINE_GROUP", 16));
+  g_.combine_group = std::max(1, EnvInt("FLASHMOE_COMBINE_GROUP", 8));
+  if ((uint64_t)g_.El * g_.cap_rows >= (1ull << 28)) {
+    MOE_ERROR_LOG("maxTokens=%d: more expert-buffer rows than a dispatch word can address", maxTokens);
+    FreeAll();
+    return cudaErrorUnknown;
+  }
   g_.queue_cap = QueueCapacity(g_, grid_);
   layout_ = MakeLayout(g_);
 
@@ -238,13 +240,7 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   CUDA_ERROR_CHECK(cudaMalloc(&act_, (size_t)g_.El * g_.cap_rows * g_.I * 2));
   CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&topk_idx_), std::max<size_t>(4, (size_t)maxTokens * g_.K * 4)));
   CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&topk_w_), std::max<size_t>(4, (size_t)maxTokens * g_.K * 4)));
-  {
-    // stride rounded to 4 entries and 16 bytes of slack: PACK reads the lists with 16-byte loads
-    const size_t list_bytes = (size_t)g_.E * AlignUp((size_t)std::max(maxTokens, 1), 4) * 4 + 16;
-    CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&send_src_), list_bytes));
-    CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&send_dst_), list_bytes));
-    CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&pack_list_), PackListBytes(g_, maxTokens)));
-  }
+  CUDA_ERROR_CHECK(cudaMalloc(reinterpret_cast<void**>(&tok_flag_), std::max<size_t>(16, (size_t)maxTokens)));
   CUDA_ERROR_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped));
   memset(status_host_, 0, 64);
   CUDA_ERROR_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_), status_host_, 0));
@@ -310,10 +306,12 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
     uint8_t* b = static_cast<uint8_t*>(peer_bases_[r]);
     FdmoePeer& pv = params_.peers[r];
     pv.ctl = reinterpret_cast<FdmoeCtl*>(b + layout_.ctl);
-    pv.slots = reinterpret_cast<FdmoeSlot*>(b + layout_.slots);
+    pv.slots[0] = reinterpret_cast<FdmoeSlot*>(b + layout_.slots[0]);
+    pv.slots[1] = reinterpret_cast<FdmoeSlot*>(b + layout_.slots[1]);
+    pv.slots[2] = reinterpret_cast<FdmoeSlot*>(b + layout_.slots[2]);
     pv.expert_cnt = reinterpret_cast<uint32_t*>(b + layout_.expert_cnt);
     pv.landed = reinterpret_cast<uint32_t*>(b + layout_.landed);
-    pv.published = reinterpret_cast<uint32_t*>(b + layout_.published);
+    pv.grp_cnt = reinterpret_cast<uint32_t*>(b + layout_.grp_cnt);
     pv.packed = b + layout_.packed;
     pv.meta = reinterpret_cast<FdmoeRowMeta*>(b + layout_.meta);
     pv.ystage = b + layout_.ystage;
@@ -330,24 +328,22 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   params_.queue_mask = (int32_t)(g_.queue_cap - 1);
   params_.combine_group = g_.combine_group;
   params_.gate_rows = 128;  // per launch: 32, 64 or 128 by token count
-  params_.debug_flags = EnvInt("FLASHMOE_DEBUG_FLAGS", 0);
+  // Two budgets for device-side waits.  Inside a launch every wait (queue, pipeline stage,
+  // accumulator) gives up after FLASHMOE_TIMEOUT_MS.  The wait for the peers to enter a launch has a
+  // budget of its own: ranks reach a collective Launch as far apart as their hosts let them (uneven
+  // batches, host work between steps, a first-call warm-up), which says nothing about a fault.
   params_.timeout_ns = (uint64_t)std::max(1, EnvInt("FLASHMOE_TIMEOUT_MS", 2000)) * 1000000ull;
+  params_.peer_timeout_ns = (uint64_t)std::max(1, EnvInt("FLASHMOE_PEER_TIMEOUT_MS", 60000)) * 1000000ull;
+  // DISPATCH tasks worked on at a time: with peers the links set the pace of the dispatch and a few
+  // workers saturate them, the others feed the tensor cores meanwhile; on one GPU every worker may
+  // copy rows.  And m-tiles per publication batch (0 = chosen per launch from the token counts).
+  params_.disp_conc = std::max(1, EnvInt("FLASHMOE_DISPATCH_WORKERS", world > 1 ? 48 : grid_));
+  params_.batch_mt = std::max(0, EnvInt("FLASHMOE_BATCH_MT", 0));
   params_.gate_w = gate_dev;
   params_.act = act_;
   params_.topk_idx = topk_idx_;
   params_.topk_w = topk_w_;
-  params_.send_src = send_src_;
-  params_.send_dst = send_dst_;
-  params_.pack_list = pack_list_;
-  // PACK tasks outstanding at a time.  On one GPU packing is bound by memory writes and is fastest with
-  // every worker on it at once; across GPUs a window leaves workers for the FFN1 tiles of landed
-  // experts while rows are still crossing NVLink.
-  params_.pack_window = std::max(1, EnvInt("FLASHMOE_PACK_WINDOW", world > 1 ? 128 : (1 << 30)));
-  // Packing starts while nearly tied tokens are still re-gated (measured faster on one and on two GPUs;
-  // 0 holds it back until every rank has gated).
-  params_.pack_early = EnvInt("FLASHMOE_PACK_EARLY", 1) != 0;
-  params_.send_stride = (int32_t)AlignUp((size_t)std::max(maxTokens, 1), 4);
-  params_.send_cnt = reinterpret_cast<uint32_t*>(arena_ + layout_.send_cnt);
+  params_.tok_flag = tok_flag_;
   params_.ffn1_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn1_done);
   params_.ffn2_done = reinterpret_cast<uint32_t*>(arena_ + layout_.ffn2_done);
   params_.status_host = status_dev_;
@@ -402,8 +398,10 @@ cudaError_t MoeKernelLauncher::LaunchBf16(const void* tokens, void* output, int 
     // the token matrix moves between launches: its TMA descriptor is rebuilt (host-only arithmetic)
     // GATE tile height: the smallest of 32/64/128 tokens that still gives every SM at most one tile,
     // so that the gate phase spreads over as many SMs as possible
+    // (with peers: always 32, many small tiles let the tensor cores start on the first rows while
+    // later tiles are still being dispatched over NVLink)
     int rows = 128;
-    if (tokensNum <= 32 * grid_) rows = 32;
+    if (tokensNum <= 32 * grid_ || world_ > 1) rows = 32;
     else if (tokensNum <= 64 * grid_) rows = 64;
     p.gate_rows = EnvInt("FLASHMOE_GATE_ROWS", rows);
     if (p.gate_rows != 32 && p.gate_rows != 64 && p.gate_rows != 128) p.gate_rows = rows;
@@ -555,16 +553,18 @@ cudaError_t MoeKernelLauncher::PrefillTasks(const std::vector<FdmoeSlot>& tasks,
   if (pipe_.ready) CUDA_ERROR_CHECK(cudaStreamSynchronize(pipe_.s_run));
   FdmoeCtl ctl;
   CUDA_ERROR_CHECK(cudaMemcpy(&ctl, arena_ + layout_.ctl, sizeof(ctl), cudaMemcpyDeviceToHost));
-  const uint32_t head = ctl.q_head;
-  FdmoeSlot* slots = reinterpret_cast<FdmoeSlot*>(arena_ + layout_.slots);
+  const uint32_t head = ctl.q[1].head;
+  FdmoeSlot* slots = reinterpret_cast<FdmoeSlot*>(arena_ + layout_.slots[1]);
   for (size_t i = 0; i < tasks.size(); ++i) {
     FdmoeSlot s = tasks[i];
     const uint32_t ticket = head + (uint32_t)i;
     s.seq = ticket + 1u;
     CUDA_ERROR_CHECK(cudaMemcpy(&slots[ticket & (g_.queue_cap - 1)], &s, sizeof(s), cudaMemcpyHostToDevice));
   }
-  const uint32_t new_head = head + (uint32_t)tasks.size();
-  return cudaMemcpy(arena_ + layout_.ctl + offsetof(FdmoeCtl, q_head), &new_head, 4, cudaMemcpyHostToDevice);
+  FdmoeQueueCtl q1 = ctl.q[1];
+  q1.head = head + (uint32_t)tasks.size();
+  q1.avail += (uint32_t)tasks.size();
+  return cudaMemcpy(arena_ + layout_.ctl + offsetof(FdmoeCtl, q) + sizeof(FdmoeQueueCtl), &q1, 12, cudaMemcpyHostToDevice);
 }
 
 cudaError_t MoeKernelLauncher::TestTaskSystem(int32_t* data, int n, cudaStream_t stream) {
@@ -621,6 +621,9 @@ cudaError_t MoeKernelLauncher::TestQueueGemm(const uint32_t* rowsPerExpert, cons
 // =============================================================== C exports
 namespace {
 const moe::MoeConfig kQwen3_30B_A3B = {2048, 768, 128, 8, moe::MOE_DTYPE_BF16, {0, 0, 0}};
+// What the reference's CreateLauncher means: its compile-time layer (src/hip/common/metadata.h:7-13)
+// with fp32 weights, tokens and output (python/pyMoeLauncherTorch.cpp:24-31).
+const moe::MoeConfig kReferenceLayer = {2048, 768, 128, 8, moe::MOE_DTYPE_FP32, {0, 0, 0}};
 
 cudaError_t CreateImpl(moe::IMoeKernelLauncher** launcher, const void* gateW, const void* w13, const void* w2,
                        int maxTokens, cudaStream_t stream, const moe::DistributedUniqueId& uid, int rank,
@@ -651,7 +654,7 @@ extern "C" cudaError_t CreateLauncher(moe::IMoeKernelLauncher** launcher, const 
                                       int maxTokens, cudaStream_t stream, const moe::DistributedUniqueId& uid,
                                       int rank, int worldSize) {
   return CreateImpl(launcher, gateWeights, ffn1ExpertWeights, ffn2ExpertWeights, maxTokens, stream, uid, rank,
-                    worldSize, kQwen3_30B_A3B);
+                    worldSize, kReferenceLayer);
 }
 
 extern "C" cudaError_t CreateLauncherEx(moe::IMoeKernelLauncher** launcher, const void* gateWeights,

@@ -1,20 +1,24 @@
 // The persistent MoE-layer kernel for sm_100a and its thin C ABI.
 //
-// One CTA per SM, every CTA a worker that pulls tasks from a ticket-based global
-// queue and overlaps these kinds of work:
-//   GATE    token tile: gate GEMM on tcgen05, top-k, softmax, row reservation in
-//           the owners' expert buffers and entries in this rank's per-expert send
-//           lists (tokens whose leading logits are nearly tied are recomputed by a
-//           GATEFIX task with fp32 FMAs in the reference's accumulation order, so
-//           the selection is the reference's);
-//   GATED   all ranks have gated: lays out this rank's PACK tasks, expert by expert;
-//   PACK    up to 72 rows of one expert: bulk copies into the owner's expert buffer;
-//           the sender that completes an expert publishes its FFN1 tiles;
-//   FFN1/2  128-row expert tiles on tcgen05 with TMEM accumulators fed by TMA
-//           (SwiGLU epilogue; routing-weight epilogue stored on the home rank);
-//   COMBINE token group: ordered sum of the K weighted rows.
-// Cross-GPU traffic is plain stores, bulk stores and scoped atomics into peers'
-// symmetric buffers.
+// One CTA per SM, every CTA a worker that takes tasks from the rank's two task queues (queue 0
+// before queue 1) or claims the next GATE tile, and overlaps these kinds of work:
+//   GATE    token tile: gate GEMM on tcgen05, top-k, softmax, row reservation in the owners'
+//           expert buffers, then the dispatch of the tile's rows: every token row is brought
+//           into shared memory once and goes out as K bulk copies, one per selected expert,
+//           into the owner's buffer (local, or a peer's over NVLink).  Tokens whose leading
+//           logits are nearly tied are recomputed by a GATEFIX task with fp32 FMAs in the
+//           reference's accumulation order, so the selection is the reference's;
+//   FFN1/2  128-row expert tiles on tcgen05 with TMEM accumulators fed by TMA (SwiGLU epilogue;
+//           routing-weight epilogue stored on the token's home rank).  The sender whose rows
+//           complete a batch of m-tiles of an expert publishes the batch's FFN1 tiles on the
+//           owner's queue; what is left when every rank has gated is published by the owner's
+//           GATED task, expert by expert;
+//   COMBINE token group: ordered sum of the K weighted rows, published by whoever delivers the
+//           group's last row.
+// Cross-GPU traffic is plain stores, bulk stores and relaxed system-scope atomics into peers'
+// symmetric buffers.  System-scope fences cost microseconds on this hardware (several times more
+// while host copies are in flight), so they are issued once per task that talked to a peer, never
+// per row or per tile of local work.
 //
 // Counterparts in the reference project (HIP, MI300X):
 //   persistent kernel + phases     src/hip/kernel/moeKernel.h:37-107
@@ -49,7 +53,7 @@ constexpr int kStageB = 256 * FDMOE_TILE_K * 2;           // 32 KB
 constexpr int kStageBytes = kStageA + kStageB;            // 48 KB
 constexpr int kRing = 3;
 constexpr int kFixBlocks = 3;  // k-blocks of gate weights per stage in a GATEFIX task (3 x 16 KB)
-constexpr int kDone = 4;  // depth of the hand-off ring to the completion warp
+constexpr int kDone = 8;  // depth of the hand-off ring to the completion warp
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = 256;
 
@@ -73,7 +77,9 @@ struct __align__(64) SmemCtl {
   uint32_t prof_n;
   uint32_t n_flagged;
   uint32_t pre[16];  // GATED scratch: per-warp totals
-  uint32_t run_round2;  // set by a task body that found this rank's second GATED round due: the group runs it next
+  uint32_t run_round2;  // set by a task body that found this rank's GATED round due: the group runs it next
+  uint32_t batch_mt;    // m-tiles per publication batch of this launch (identical on all ranks)
+  uint32_t tokens_all;  // tokens of all ranks this launch
   // Copy of the kernel parameters for the task bodies that are compiled as separate functions:
   // there the parameter block is only reachable through a generic pointer, and every access to
   // the constant bank through one costs on the order of a hundred cycles; shared memory does not.
@@ -87,7 +93,6 @@ struct __align__(64) SmemCtl {
       // GATE task scratch (per expert / per token of the tile)
       uint32_t cnt[128];
       uint32_t base[128];
-      uint32_t sbase[128];                      // first send-list entry of the tile per expert
       uint32_t flagged[FDMOE_GATE_TOKENS];
       uint8_t isflag[FDMOE_GATE_TOKENS];
       float logit_tile[32][132];                // one 32-token quarter of the logits (padded rows)
@@ -299,110 +304,129 @@ __device__ __forceinline__ bool wait_idle(const FdmoeParams& p, SmemCtl& sc, uin
   return true;
 }
 
-// ------------------------------------------------------------- global queue
-// Producers take `n` consecutive tickets with one atomic add on head, fill the
-// slots and publish each with a release store of ticket+1.
+// ------------------------------------------------------------- task queues
+// A rank has two queues.  Producers (this rank's workers and, for queue slots in the symmetric
+// arena, its peers) take `n` consecutive tickets with one atomic add on head, fill the slots,
+// publish each with a store of ticket + 1 after one fence, and then add `n` to the queue's count of
+// available tasks.  Consumers (this rank's workers only) first take one unit of that count (giving
+// it back if there was none), and only then a ticket from tail: a consumer never holds a ticket
+// for a task that does not exist yet, so it can always turn to the other queue, and no
+// compare-and-swap loop serialises the workers.
+// `S`: the queue belongs to a peer (system-scope atomics and fence), else to this GPU.
 template <bool S, class Gen>
-__device__ __forceinline__ void queue_push(const FdmoeParams& p, const FdmoePeer& q, uint32_t n,
-                                           Gen gen) {
-  const uint32_t t0 = atom_add<S>(&q.ctl->q_head, n);
+__device__ __forceinline__ void queue_push(const FdmoeParams& p, const FdmoePeer& q, int qi, uint32_t n, Gen gen) {
+  const uint32_t t0 = atom_add<S>(&q.ctl->q[qi].head, n);
+  FdmoeSlot* slots = q.slots[qi];
   for (uint32_t i = 0; i < n; ++i) {
-    FdmoeSlot* s = &q.slots[(t0 + i) & (uint32_t)p.queue_mask];
+    FdmoeSlot* s = &slots[(t0 + i) & (uint32_t)p.queue_mask];
     uint32_t a, b, c;
     gen(i, a, b, c);
     s->a = a;
     s->b = b;
     s->c = c;
   }
-  // one fence orders every payload (and whatever the caller wrote before) ahead of the
-  // sequence words; a release store per slot would pay for a fence each time
+  // one fence orders every payload (and whatever the caller wrote or observed before) ahead of
+  // the sequence words; a release store per slot would pay for a fence each time
   fence_acqrel<S>();
-  for (uint32_t i = 0; i < n; ++i) st_relaxed<S>(&q.slots[(t0 + i) & (uint32_t)p.queue_mask].seq, t0 + i + 1u);
+  for (uint32_t i = 0; i < n; ++i) st_relaxed<S>(&slots[(t0 + i) & (uint32_t)p.queue_mask].seq, t0 + i + 1u);
+  atom_add<S>(&q.ctl->q[qi].avail, n);
 }
 
-// Tokens per COMBINE task of a rank with T tokens: at most `cap`, and such that the tasks fill
-// whole waves of `grid` workers (e.g. 4096 tokens on 148 workers: 14 tokens, 293 tasks, two
-// waves).  A pure function of T, so that a peer can publish another rank's COMBINE tasks.
-__device__ __forceinline__ uint32_t combine_group_of(int T, int grid, int cap) {
-  if (T <= 0) return 1u;
-  const int waves = (T + cap * grid - 1) / (cap * grid);
-  const int g = (T + waves * grid - 1) / (waves * grid);
-  return (uint32_t)max(1, min(g, cap));
+// Push onto the queue of rank `r`: system scope only when that is another GPU.
+template <bool S, class Gen>
+__device__ __forceinline__ void queue_push_rank(const FdmoeParams& p, int r, int qi, uint32_t n, Gen gen) {
+  if (S && r != p.rank)
+    queue_push<true>(p, p.peers[r], qi, n, gen);
+  else
+    queue_push<false>(p, p.peers[r], qi, n, gen);
 }
 
 __device__ __forceinline__ uint32_t task_word(uint32_t kind, uint32_t e, uint32_t n) {
   return kind | (e << 8) | (n << 20);
 }
 
-// Consumer (single thread).  A task in the rank's urgent word goes first; otherwise take a
-// ticket and wait (bounded) until its slot is published or the queue is closed.  While it waits
-// the consumer also serves the urgent word; the ticket it holds then stays with it
-// (`has_ticket`) and is waited for on the next call.
-// Urgent word: 0 = none, else 0x80000000 | kind | b << 8.  It carries the GATED tasks, which must
-// not queue up behind the hundreds of PACK tasks they publish.
-__device__ __forceinline__ FdmoeSlot urgent_task(uint32_t word) {
-  FdmoeSlot out;
-  out.seq = 0;
-  out.a = word & 0xffu;
-  out.b = (word >> 8) & 0xffu;
-  out.c = 0;
-  return out;
-}
-template <bool S>
-__device__ __forceinline__ void push_urgent(const FdmoeParams& p, const FdmoePeer& q, uint32_t kind, uint32_t b) {
-  fence_acqrel<S>();
-  const uint32_t old = atom_exch<S>(&q.ctl->urgent, 0x80000000u | kind | (b << 8));
-  if (old != 0u) {  // (never two at a time by construction; do not lose it if it happens)
-    queue_push<S>(p, q, 1u, [old](uint32_t, uint32_t& a, uint32_t& bb, uint32_t& c) {
-      a = old & 0xffu;
-      bb = (old >> 8) & 0xffu;
-      c = 0;
-    });
-  }
-}
-template <bool S>
-__device__ __forceinline__ FdmoeSlot queue_pop(const FdmoeParams& p, SmemCtl& sc, uint32_t& ticket, bool& has_ticket) {
-  const FdmoePeer& me = p.peers[p.rank];
+__device__ __forceinline__ FdmoeSlot exit_task() {
   FdmoeSlot out;
   out.seq = 0;
   out.a = FDMOE_TASK_EXIT;
   out.b = 0;
   out.c = 0;
-  if (sc.abort) return out;
-  if (!has_ticket) {
-    if (ld_relaxed<S>(&me.ctl->urgent) != 0u) {
-      const uint32_t u = atom_exch<S>(&me.ctl->urgent, 0u);
-      if (u != 0u) return urgent_task(u);
-    }
-    ticket = atomicAdd(&me.ctl->q_tail, 1u);
-    has_ticket = true;
-  }
-  FdmoeSlot* s = &me.slots[ticket & (uint32_t)p.queue_mask];
-  const uint64_t t0 = ptx::globaltimer_ns();
-  uint32_t spins = 0;
-  for (;;) {
-    if (ld_acquire<S>(&s->seq) == ticket + 1u) break;
-    if (ld_relaxed<S>(&me.ctl->closed) != 0u || sc.abort) return out;
-    if (ld_relaxed<S>(&me.ctl->urgent) != 0u) {
-      const uint32_t u = atom_exch<S>(&me.ctl->urgent, 0u);
-      if (u != 0u) return urgent_task(u);
-    }
-    if ((++spins & 15u) == 0u) {
-      if (ptx::globaltimer_ns() - t0 > p.timeout_ns) {
-        raise_error(p, sc, FDMOE_ERR_TIMEOUT_QUEUE, (blockIdx.x << 8));
-        return out;
-      }
-      __nanosleep(100);
-    }
-  }
-  has_ticket = false;
-  out.a = s->a;
-  out.b = s->b;
-  out.c = s->c;
   return out;
 }
 
-// Closes this rank's queue once GATED has run, every m-tile of its experts
+// Takes the oldest task of queue `qi` of this rank if there is one (single thread).  Returns
+// false when the queue is empty (or on an error, with sc.abort raised).
+template <bool S>
+__device__ __forceinline__ bool try_pop(const FdmoeParams& p, SmemCtl& sc, int qi, FdmoeSlot& out) {
+  const FdmoePeer& me = p.peers[p.rank];
+  FdmoeQueueCtl* q = &me.ctl->q[qi];
+  if ((int32_t)ld_relaxed<S>(&q->avail) <= 0) return false;
+  if ((int32_t)atomicSub(&q->avail, 1u) <= 0) {
+    atomicAdd(&q->avail, 1u);  // others were faster: give the unit back
+    return false;
+  }
+  // one published task is ours: its ticket (tickets are published in order of completion of the
+  // pushes, so the slot of this ticket may still be a moment away)
+  const uint32_t t = atomicAdd(&q->tail, 1u);
+  FdmoeSlot* s = &me.slots[qi][t & (uint32_t)p.queue_mask];
+  const uint64_t t0 = ptx::globaltimer_ns();
+  uint32_t spins = 0;
+  while (ld_acquire<S>(&s->seq) != t + 1u) {
+    if ((++spins & 15u) == 0u) {
+      if (sc.abort) return false;
+      if (ptx::globaltimer_ns() - t0 > p.timeout_ns) {
+        raise_error(p, sc, FDMOE_ERR_TIMEOUT_QUEUE, (blockIdx.x << 8) | 1u);
+        return false;
+      }
+    }
+  }
+  out.seq = 0;
+  out.a = s->a;
+  out.b = s->b;
+  out.c = s->c;
+  return true;
+}
+
+// The next task of this worker (single thread): queue 0 first; then a DISPATCH task unless enough
+// workers are dispatching already (across GPUs the links set the pace of the dispatch, a few workers
+// saturate them while the others feed the tensor cores); then a GATE tile; then queue 1.
+// Waits (bounded) while there is nothing to do and the rank's work is not finished.
+template <bool S>
+__device__ __forceinline__ FdmoeSlot next_task(const FdmoeParams& p, SmemCtl& sc, uint32_t gate_tiles) {
+  FdmoeCtl* ctl = p.peers[p.rank].ctl;
+  FdmoeSlot out;
+  const uint64_t t0 = ptx::globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    if (sc.abort) return exit_task();
+    if (try_pop<S>(p, sc, 0, out)) return out;
+    if ((int32_t)ld_relaxed<false>(&ctl->q[2].avail) > 0 && ld_relaxed<false>(&ctl->disp_active) < (uint32_t)p.disp_conc) {
+      if (atomicAdd(&ctl->disp_active, 1u) < (uint32_t)p.disp_conc && try_pop<false>(p, sc, 2, out)) return out;
+      atomicSub(&ctl->disp_active, 1u);
+    }
+    if (gate_tiles != 0u && ld_relaxed<false>(&ctl->gate_next) < gate_tiles) {
+      const uint32_t g = atomicAdd(&ctl->gate_next, 1u);
+      if (g < gate_tiles) {
+        out.seq = 0;
+        out.a = FDMOE_TASK_GATE;
+        out.b = g;
+        out.c = 0;
+        return out;
+      }
+    }
+    if (try_pop<S>(p, sc, 1, out)) return out;
+    if (ld_relaxed<false>(&ctl->closed) != 0u) return exit_task();
+    if ((++spins & 15u) == 0u) {
+      if (ptx::globaltimer_ns() - t0 > p.timeout_ns) {
+        raise_error(p, sc, FDMOE_ERR_TIMEOUT_QUEUE, (blockIdx.x << 8));
+        return exit_task();
+      }
+    }
+    __nanosleep(spins < 64u ? 40 : 200);
+  }
+}
+
+// Closes this rank's queues once GATED has run, every m-tile of its experts
 // has finished FFN2 and every token of this rank has been combined.  Called
 // after each of those three kinds of event; the sequentially-consistent fence
 // guarantees that the last caller sees the other two conditions.
@@ -415,42 +439,92 @@ __device__ __forceinline__ void maybe_close(const FdmoeParams& p) {
   st_release<false>(&ctl->closed, 1u);
 }
 
-// The routing of every token of this rank is decided (rows reserved on their
-// owners, send lists complete): tell every rank; whoever completes a rank's
-// count hands it the GATED task, from which its row counts are final.
-// Two things must have happened before rank q's second GATED round may run: every rank has gated,
-// and rank q has laid out its first round (a rank without tokens has none and counts both at once).
-// Whoever brings the count to two hands rank q the task.
-// `sc` non-null: the caller is thread 0 of an epilogue group at the end of a task; if the round
-// falls to its own rank the group runs it right away (flag run_round2) instead of queueing it.
+// m-tiles per publication batch of a launch with `tokens_all` tokens over all ranks.  A sender
+// that completes a batch of an expert publishes its FFN1 tiles at once, so the tensor cores
+// start while rows are still travelling; every batch of an expert re-reads the expert's weights,
+// which is cheap when a rank holds few experts (their weights stay in L2) and expensive when it
+// holds all of them.  One GPU: no batches, every expert is published whole once gating has
+// finished.  More GPUs: about `world` batches per expert, at least two m-tiles each.
+// A pure function of values every rank knows, so that all ranks agree.
+__device__ __forceinline__ uint32_t batch_mt_of(const FdmoeParams& p, uint32_t tokens_all) {
+  if (p.batch_mt > 0) return (uint32_t)min(p.batch_mt, p.MT);
+  if (p.world == 1) return (uint32_t)p.MT;
+  const uint32_t mt_expert = (uint32_t)(((uint64_t)tokens_all * p.K / p.E) / FDMOE_TILE_M);
+  const uint32_t b = mt_expert / (uint32_t)p.world;
+  if (b < 2u) return (uint32_t)p.MT;
+  return min(min(b, 8u), (uint32_t)p.MT);
+}
+
+// Tokens of rank `r` in this launch.
+__device__ __forceinline__ uint32_t tokens_of_rank(const FdmoeParams& p, int r) {
+  if (r == p.rank) return (uint32_t)p.T;
+  return ld_relaxed<false>(&p.peers[p.rank].ctl->tokens_of[p.epoch & 1u][r]);
+}
+
+// All rows [b * B * 128, (b + 1) * B * 128) of local expert `le` of rank `owner` have landed: the FFN1
+// tiles of those B m-tiles go onto the owner's queue 1, m-tile major (single thread; the caller
+// observed the landing counter, the fence inside the push orders the rows before the tasks).
 template <bool S>
-__device__ __forceinline__ void second_round_ready(const FdmoeParams& p, SmemCtl* sc, int q, uint32_t n) {
+__device__ __forceinline__ void publish_batch(const FdmoeParams& p, int owner, uint32_t le, uint32_t b, uint32_t B) {
+  const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
+  queue_push_rank<S>(p, owner, 1, B * nt1, [&](uint32_t i, uint32_t& a, uint32_t& bb, uint32_t& c) {
+    const uint32_t j = i / nt1;
+    a = task_word(FDMOE_TASK_FFN1, le, i - j * nt1);
+    bb = b * B + j;
+    c = 128u;
+  });
+}
+
+// `n` more rows [row0, row0 + n) of local expert `le` of rank `owner` have landed (n <= 128, the rows
+// lie in one or two batches).  The caller has made the rows visible (fence) before.  Publishes
+// every batch this completes.
+template <bool S>
+__device__ __forceinline__ void rows_landed(const FdmoeParams& p, uint32_t B, int owner, uint32_t le, uint32_t row0,
+                                            uint32_t n) {
+  const uint32_t RB = B * FDMOE_TILE_M;
+  const FdmoePeer& op = p.peers[owner];
+  const uint32_t b0 = row0 / RB;
+  const uint32_t n0 = min(n, (b0 + 1u) * RB - row0);
+  if (atom_add<S>(&op.landed[(size_t)le * p.MT + b0], n0) + n0 == RB) publish_batch<S>(p, owner, le, b0, B);
+  if (n > n0) {
+    if (atom_add<S>(&op.landed[(size_t)le * p.MT + b0 + 1u], n - n0) + (n - n0) == RB)
+      publish_batch<S>(p, owner, le, b0 + 1u, B);
+  }
+}
+
+// The routing of every token of this rank is decided and its rows have landed on their owners:
+// tell every rank.  Whoever brings a rank's count to the world size hands it the GATED task (its
+// row counts are final); if that is the caller's own rank and `sc` is given, the caller's
+// epilogue group runs it next (flag run_round2).  Called by one full warp.
+template <bool S>
+__device__ __forceinline__ void gating_finished(const FdmoeParams& p, SmemCtl* sc, int lane) {
   fence_acqrel<S>();
-  const uint32_t prev = atom_add<S>(&p.peers[q].ctl->round2_rdv, n);
-  if (prev + n == 2u) {
-    if (sc && q == p.rank)
+  uint32_t prev = 0u;
+  if (lane < p.world) prev = atom_add<S>(&p.peers[lane].ctl->ranks_gated, 1u);
+  const bool last = lane < p.world && prev == (uint32_t)p.world - 1u;
+  if (last) {
+    if (sc && lane == p.rank)
       sc->run_round2 = 1u;
     else
-      push_urgent<S>(p, p.peers[q], FDMOE_TASK_GATED, 0u);  // second round
+      queue_push_rank<S>(p, lane, 0, 1u, [](uint32_t, uint32_t& a, uint32_t& b, uint32_t& c) {
+        a = FDMOE_TASK_GATED;
+        b = 0;
+        c = 0;
+      });
   }
+  __syncwarp();
 }
 
+// Counts `n` tokens of this rank as gated; the caller has landed their rows.  Called by one full warp.
 template <bool S>
-__device__ void gating_finished(const FdmoeParams& p, SmemCtl* sc) {
-  for (int q = 0; q < p.world; ++q) {
-    fence_acqrel<S>();
-    const uint32_t prev = atom_add<S>(&p.peers[q].ctl->ranks_gated, 1u);
-    // rank q's second round starts when every rank has gated and its own first round is laid out
-    if (prev == (uint32_t)p.world - 1u) second_round_ready<S>(p, sc, q, 1u);
+__device__ __forceinline__ void count_gated(const FdmoeParams& p, SmemCtl& sc, int lane, uint32_t n) {
+  uint32_t done = 0u;
+  if (lane == 0) {
+    fence_acqrel<false>();
+    done = atomicAdd(&p.peers[p.rank].ctl->gated_tokens, n) + n;
   }
-}
-
-// Counts `n` tokens of this rank as gated; the caller has written their send-list entries.
-template <bool S>
-__device__ __forceinline__ void count_gated(const FdmoeParams& p, SmemCtl& sc, uint32_t n) {
-  fence_acqrel<S>();
-  const uint32_t done = atomicAdd(&p.peers[p.rank].ctl->gated_tokens, n) + n;
-  if (n && done == (uint32_t)p.T) gating_finished<S>(p, &sc);
+  done = __shfl_sync(0xffffffffu, done, 0);
+  if (n && done == (uint32_t)p.T) gating_finished<S>(p, &sc, lane);
 }
 
 // Monotonic unsigned key of a float (larger float <=> larger key; -0 counts as +0).
@@ -559,9 +633,13 @@ __device__ __forceinline__ void topk_warp(const float* logits, int E, int K, int
 // scale (more than ten times that difference on each side) is handed to a
 // GATEFIX task, which recomputes its logits in the reference's order; for every
 // other token both orders select the same experts in the same order.
+//
+// The selection and the routing weights go to global memory, and a DISPATCH task for the tile's
+// tokens onto queue 2.
 template <bool S>
-__device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, uint64_t* tmem_empty_bar,
-                                           int q, int h, int lane, int etid, int ewarp, uint32_t tile) {
+__device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr,
+                                           uint64_t* tmem_empty_bar, int q, int h, int lane, int etid, int ewarp,
+                                           uint32_t tile) {
   const int E = p.E, K = p.K;
   const int t0 = (int)tile * p.gate_rows;
   const int nt = min(p.gate_rows, p.T - t0);
@@ -570,7 +648,7 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
 
   if (etid < 128) sc.cnt[etid] = 0;
   if (etid == 0) sc.n_flagged = 0;
-  // ---- four passes, one per TMEM lane quadrant: the two warps that may read the
+  // ---- one pass per TMEM lane quadrant: the two warps that may read the
   // quadrant spill its 32 rows to shared memory, then every warp extracts the
   // top-9 of four rows with warp-wide arg-max rounds
   prof_mark(p, sc, etid, 40);
@@ -631,232 +709,185 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
   }
   epi_bar();
   prof_mark(p, sc, etid, 3);
-  if (etid < nt && !sc.isflag[etid]) {
-    // softmax over the K kept logits in the reference's order: the values are descending, so
-    // the running max is the first one and the sum is 1 + e_1 + e_2 + ... (reference
-    // refSoftmax.h:23-50, which works in double; fp32 with the accurate expf stays within 3e-7 of
-    // it, far inside the 1e-5 the routing weights are held to, and costs a tenth of the time)
-    const float m = sc.top_v[etid][0];
-    float ex[FDMOE_MAX_TOPK];
-    float sum = 1.0f;
-#pragma unroll
-    for (int k = 0; k < FDMOE_MAX_TOPK; ++k) {
-      if (k < K) {
-        ex[k] = expf(sc.top_v[etid][k] - m);
-        if (k > 0) sum += ex[k];
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < FDMOE_MAX_TOPK; ++k) {
-      if (k < K) {
-        const int e = sc.top_i[etid][k];
-        const float w = ex[k] / sum;
-        sc.tk_w[etid][k] = w;
-        sc.lpos[etid][k] = (uint8_t)atomicAdd(&sc.cnt[e], 1u);
-        p.topk_idx[(size_t)(t0 + etid) * K + k] = e;
-        p.topk_w[(size_t)(t0 + etid) * K + k] = w;
-      }
-    }
-  }
-  epi_bar();
-  prof_mark(p, sc, etid, 5);
-  // reserve rows in the owners' expert buffers and entries in this rank's send
-  // lists: one atomic each per expert and tile
-  if (etid < E) {
-    const uint32_t cnt = sc.cnt[etid];
-    if (cnt) {
-      const int owner = etid / p.El, le = etid - owner * p.El;
-      const uint32_t base = atom_add<S>(&p.peers[owner].expert_cnt[le], cnt);
-      if (base + cnt > (uint32_t)p.cap_rows) raise_error(p, sc, FDMOE_ERR_ROW_OVERFLOW, etid);
-      sc.base[etid] = base;
-      sc.sbase[etid] = atomicAdd(&p.send_cnt[etid], cnt);
-    }
-  }
-  epi_bar();
-  prof_mark(p, sc, etid, 6);
-  if (etid < nt && !sc.isflag[etid] && !sc.abort) {
-    for (int k = 0; k < K; ++k) {
-      const int e = sc.top_i[etid][k];
-      const int owner = e / p.El, le = e - owner * p.El;
-      const size_t rowg = (size_t)le * p.cap_rows + sc.base[e] + sc.lpos[etid][k];
-      const size_t ent = (size_t)e * p.send_stride + sc.sbase[e] + sc.lpos[etid][k];
-      p.send_src[ent] = ((t0 + etid) << 4) | k;
-      p.send_dst[ent] = (int32_t)rowg;
-      // FdmoeRowMeta {token, home << 8 | slot, weight, pad} as one 16-byte store
-      *reinterpret_cast<uint4*>(&p.peers[owner].meta[rowg]) =
-          make_uint4((uint32_t)(t0 + etid), (uint32_t)((p.rank << 8) | k), __float_as_uint(sc.tk_w[etid][k]), 0u);
-    }
-  }
-  epi_bar();
-  prof_mark(p, sc, etid, 7);
+  // nearly tied tokens go to GATEFIX tasks right away (queue 0: idle workers take them at once),
+  // so that they are re-gated while this tile dispatches its rows
   if (etid == 0 && !sc.abort) {
     const uint32_t nf = sc.n_flagged, nfix = (nf + 1u) / 2u;
     if (nfix) {
-      fence_acqrel<false>();
-      queue_push<false>(p, p.peers[p.rank], nfix, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
+      queue_push<false>(p, p.peers[p.rank], 0, nfix, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
         a = FDMOE_TASK_GATEFIX;
         b = (uint32_t)t0 + sc.flagged[2 * i];
         c = (2 * i + 1 < nf) ? (uint32_t)t0 + sc.flagged[2 * i + 1] : 0xffffffffu;
       });
     }
-    count_gated<S>(p, sc, (uint32_t)nt - nf);
-    // the last GATE tile of this rank: its rows so far (all but those of nearly tied tokens) can be packed
-    const uint32_t tiles = (uint32_t)((p.T + p.gate_rows - 1) / p.gate_rows);
-    fence_acqrel<false>();
-    if (atomicAdd(&p.peers[p.rank].ctl->gate_tiles_done, 1u) + 1u == tiles) {
-      if (p.pack_early)
-        push_urgent<false>(p, p.peers[p.rank], FDMOE_TASK_GATED, 1u);  // first round now
-      else
-        second_round_ready<S>(p, &sc, p.rank, 1u);  // both rounds once every rank has gated
+  }
+  if (etid < nt) {
+    if (!sc.isflag[etid]) {
+      // softmax over the K kept logits in the reference's order: the values are descending, so
+      // the running max is the first one and the sum is 1 + e_1 + e_2 + ... (reference
+      // refSoftmax.h:23-50, which works in double; fp32 with the accurate expf stays within 3e-7 of
+      // it, far inside the 1e-5 the routing weights are held to, and costs a tenth of the time)
+      const float m = sc.top_v[etid][0];
+      float ex[FDMOE_MAX_TOPK];
+      float sum = 1.0f;
+#pragma unroll
+      for (int k = 0; k < FDMOE_MAX_TOPK; ++k) {
+        if (k < K) {
+          ex[k] = expf(sc.top_v[etid][k] - m);
+          if (k > 0) sum += ex[k];
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < FDMOE_MAX_TOPK; ++k) {
+        if (k < K) {
+          p.topk_idx[(size_t)(t0 + etid) * K + k] = sc.top_i[etid][k];
+          p.topk_w[(size_t)(t0 + etid) * K + k] = ex[k] / sum;
+        }
+      }
     }
+    p.tok_flag[t0 + etid] = sc.isflag[etid];  // 1: the token's GATEFIX task routes and sends it
+  }
+  epi_bar();
+  prof_mark(p, sc, etid, 5);
+  if (etid == 0 && !sc.abort) {
+    // (the fence inside the push orders the routing written by the other threads before the barrier
+    // ahead of the task)
+    queue_push<false>(p, p.peers[p.rank], 2, 1u, [&](uint32_t, uint32_t& a, uint32_t& b, uint32_t& c) {
+      a = FDMOE_TASK_DISPATCH;
+      b = (uint32_t)t0;
+      c = (uint32_t)nt;
+    });
   }
 }
 
-// ===================================================================== PACK
-// Sends `count` rows of one expert (entries [first, first + count) of this rank's
-// send list for it) to the expert's owner.  The rows travel as bulk copies:
-// the TMA warp brings up to pack_rows_per_stage() token rows into a pipeline
-// stage, the lanes of the first epilogue warp send one row each from there into
-// the owner's expert buffer (local, or a peer's over NVLink).  The sender whose
-// rows complete the expert while its row count is known to be final (every rank
-// has gated) publishes the expert's FFN1 tile tasks on the owner's queue; an
-// expert that completes earlier is left to the owner's second GATED round.
-__device__ __forceinline__ uint32_t pack_rows_per_stage(int H) {
+// ================================================================= DISPATCH
+// Rows of a token tile that fit one pipeline stage (the stage holds whole token rows).
+__device__ __forceinline__ uint32_t dispatch_rows_per_stage(int H) {
   return min(16u, (uint32_t)kStageBytes / ((uint32_t)H * 2u));
 }
 
-// TMA-warp side of a PACK task (one thread): brings the token rows of the piece into the
-// pipeline stages, up to pack_rows_per_stage() rows per stage.  The source indices of the
-// next stage are fetched while the current one is waited for and issued.
-__device__ __noinline__ bool pack_loads(const FdmoeParams& p, SmemCtl& sc, uint8_t* stage, uint32_t& stage_it,
-                                        uint32_t e, uint32_t first, uint32_t count) {
-  const uint32_t rowb = (uint32_t)p.H * 2u, rps = pack_rows_per_stage(p.H);
-  const int32_t* src_list = p.send_src + (size_t)e * p.send_stride + first;
-  const uint8_t* xb = reinterpret_cast<const uint8_t*>(p.x);
-  int32_t cur[16], nxt[16];
-#pragma unroll
-  for (uint32_t i = 0; i < 16; ++i) cur[i] = (i < rps && i < count) ? __ldcg(src_list + i) : 0;
-  for (uint32_t b0 = 0; b0 < count; b0 += rps, ++stage_it) {
-    const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
-    const uint32_t nrows = min(rps, count - b0);
-#pragma unroll
-    for (uint32_t i = 0; i < 16; ++i) nxt[i] = (i < rps && b0 + rps + i < count) ? __ldcg(src_list + b0 + rps + i) : 0;
-    if (!wait_bar(p, sc, &sc.empty_bar[s], sph ^ 1u, FDMOE_ERR_TIMEOUT_STAGE)) return false;
-    ptx::mbar_expect_tx(&sc.full_bar[s], nrows * rowb);
-#pragma unroll
-    for (uint32_t i = 0; i < 16; ++i)
-      if (i < nrows)
-        ptx::bulk_load_1d(stage + s * kStageBytes + i * rowb, xb + (size_t)(cur[i] >> 4) * rowb, rowb, &sc.full_bar[s]);
-#pragma unroll
-    for (uint32_t i = 0; i < 16; ++i) cur[i] = nxt[i];
-  }
-  return true;
-}
-
-// All rows of local expert `le` of rank `op` have landed and their number `total` is final: its FFN1
-// tile tasks go onto that rank's queue, m-tile major, so that the tiles of one expert run together and
-// share its weights through L2.  Called by the whole epilogue group; exactly one caller per expert and
-// launch gets to publish (flag `published`).
+// Copies the rows of tokens [t0, t0 + nt) (nt <= 128) into the expert buffers of their owners.
+// First the task reserves rows: one atomic per expert on the owner's row counter.  Rows are reserved
+// when they are about to be sent, not when the tokens are gated, so that an expert's buffer fills in
+// the order of the dispatch and its first batch of m-tiles is complete long before its last.
+// Then the TMA warp brings the token rows (contiguous in the token matrix) into the pipeline stages;
+// one thread per (row of the stage, slot) writes the row's sideband and sends the row to the expert's
+// owner as one bulk copy (local, or a peer's memory over NVLink), so a token row is read once and
+// written K times.  While the copies of a stage are in flight the thread finishes the stage before
+// it: waits until its copy of that stage is written, counts the row as landed on its owner (one
+// fence first) and publishes the FFN1 tiles of a batch this completes; then the stage goes back to
+// the TMA warp.  Returns false when the group has to give up.
 template <bool S>
-__device__ __forceinline__ void publish_expert_tiles(const FdmoeParams& p, SmemCtl& sc, int etid, const FdmoePeer& op,
-                                                     uint32_t le, uint32_t total) {
-  const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
-  const uint32_t full = total / 128u, rem = total % 128u, ntask = ((total + 127u) / 128u) * nt1;
-  if (etid == 0) {
-    sc.q_total = 0u;
-    if (atom_exch<S>(&op.published[le], 1u) == 0u) {
-      fence_acqrel<S>();  // the senders' rows (observed through the counter) before the tasks
-      sc.q_t0 = atom_add<S>(&op.ctl->q_head, ntask);
-      sc.q_total = ntask;
-    }
-  }
+__device__ __noinline__ bool dispatch_task(const FdmoeParams& p, SmemCtl& sc, uint8_t* stage, uint32_t& stage_it,
+                                           int etid, int ewarp, int lane, uint32_t t0, uint32_t nt) {
+  const uint32_t K = (uint32_t)p.K;
+  const uint32_t rowb = (uint32_t)p.H * 2u, rps = dispatch_rows_per_stage(p.H);
+  const uint32_t nstage = (nt + rps - 1u) / rps;
+  const uint32_t kNoRow = 0xffffffffu;
+  if (etid < 128) sc.cnt[etid] = 0;
+  if (etid == 0) sc.n_flagged = 0;
   epi_bar();
-  if (sc.q_total) {
-    const uint32_t t0 = sc.q_t0;
-    bool any = false;
-    for (uint32_t idx = etid; idx < ntask; idx += kEpiThreads) {
-      const uint32_t j = idx / nt1, n = idx - j * nt1;
-      FdmoeSlot* sl = &op.slots[(t0 + idx) & (uint32_t)p.queue_mask];
-      sl->a = task_word(FDMOE_TASK_FFN1, le, n);
-      sl->b = j;
-      sl->c = (j < full) ? 128u : rem;
-      any = true;
-    }
-    if (any) {
-      fence_acqrel<S>();
-      for (uint32_t idx = etid; idx < ntask; idx += kEpiThreads)
-        st_relaxed<S>(&op.slots[(t0 + idx) & (uint32_t)p.queue_mask].seq, t0 + idx + 1u);
-    }
-  }
-  epi_bar();  // sc.q_t0 / sc.q_total may be rewritten only after everyone has read them
-}
-
-template <bool S>
-__device__ __noinline__ bool pack_task(const FdmoeParams& p, SmemCtl& sc, uint8_t* stage, uint32_t& stage_it, int etid,
-                                       int ewarp, int lane, uint32_t e, uint32_t first, uint32_t count) {
-  const int H = p.H;
-  const uint32_t rowb = (uint32_t)H * 2u, rps = pack_rows_per_stage(H);
-  const int owner = (int)e / p.El, le = (int)e - owner * p.El;
-  const FdmoePeer& op = p.peers[owner];
-  uint8_t* packed = reinterpret_cast<uint8_t*>(op.packed);
-  const int32_t* dst_list = p.send_dst + (size_t)e * p.send_stride + first;
-  for (uint32_t b0 = 0; b0 < count; b0 += rps, ++stage_it) {
-    const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
-    const uint32_t nrows = min(rps, count - b0);
-    int32_t d = 0;
-    if (ewarp == 0 && (uint32_t)lane < nrows) d = __ldcg(dst_list + b0 + lane);
-    if (!epi_vote_all(wait_bar(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE))) return false;
-    if (ewarp == 0) {
-      if ((uint32_t)lane < nrows) {
-        ptx::bulk_store_1d(packed + (size_t)d * rowb, stage + s * kStageBytes + (uint32_t)lane * rowb, rowb);
-        ptx::bulk_commit_group();
-        ptx::bulk_wait_group_read0();
+  if ((uint32_t)etid < nt) {
+    const bool fl = __ldcg(&p.tok_flag[t0 + etid]) != 0;
+    sc.isflag[etid] = fl ? 1 : 0;
+    if (fl) {
+      atomicAdd(&sc.n_flagged, 1u);
+    } else {
+      for (uint32_t k = 0; k < K; ++k) {
+        const int e = __ldcg(&p.topk_idx[(size_t)(t0 + etid) * K + k]);
+        sc.top_i[etid][k] = (uint8_t)e;
+        sc.lpos[etid][k] = (uint8_t)atomicAdd(&sc.cnt[e], 1u);
       }
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&sc.empty_bar[s]);
     }
   }
+  epi_bar();
+  prof_mark(p, sc, etid, 50);
+  if (etid < p.E) {
+    const uint32_t cnt = sc.cnt[etid];
+    if (cnt) {
+      const int owner = etid / p.El, le = etid - owner * p.El;
+      uint32_t base;
+      if (S && owner != p.rank)
+        base = atom_add<true>(&p.peers[owner].expert_cnt[le], cnt);
+      else
+        base = atom_add<false>(&p.peers[owner].expert_cnt[le], cnt);
+      if (base + cnt > (uint32_t)p.cap_rows) raise_error(p, sc, FDMOE_ERR_ROW_OVERFLOW, etid);
+      sc.base[etid] = base;
+    }
+  }
+  epi_bar();
+  prof_mark(p, sc, etid, 51);
+  uint32_t prev_s = 0u;
+  for (uint32_t i = 0; i < nstage; ++i, ++stage_it) {
+    const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
+    const uint32_t nrows = min(rps, nt - i * rps);
+    uint32_t my_d = kNoRow, my_w = 0u;
+    const uint32_t r = (uint32_t)etid / K, k = (uint32_t)etid - r * K;
+    const uint32_t tok = i * rps + r;  // within the task
+    if ((uint32_t)etid < nrows * K && !sc.isflag[tok] && !sc.abort) {
+      const uint32_t e = sc.top_i[tok][k];
+      const uint32_t owner = e / (uint32_t)p.El, le = e - owner * (uint32_t)p.El;
+      my_d = (owner << 28) | (le * (uint32_t)p.cap_rows + sc.base[e] + sc.lpos[tok][k]);
+      my_w = __float_as_uint(__ldcg(&p.topk_w[(size_t)(t0 + tok) * K + k]));
+    }
+    if (!epi_vote_all(wait_bar(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE))) return false;
+    prof_mark(p, sc, etid, 52);
+    if (my_d != kNoRow) {
+      const FdmoePeer& op = p.peers[my_d >> 28];
+      const uint32_t rowg = my_d & 0x0fffffffu;
+      // FdmoeRowMeta {token, home << 8 | slot, weight, pad} as one 16-byte store
+      *reinterpret_cast<uint4*>(&op.meta[rowg]) = make_uint4(t0 + tok, (uint32_t)((p.rank << 8) | k), my_w, 0u);
+      ptx::bulk_store_1d(reinterpret_cast<uint8_t*>(op.packed) + (size_t)rowg * rowb,
+                         stage + s * kStageBytes + r * rowb, rowb);
+    }
+    ptx::bulk_commit_group();
+    if (i > 0u) {
+      ptx::bulk_wait_group_read1();  // this thread's copy of the stage before this one has read its row
+      epi_bar();
+      if (etid == 0) ptx::mbar_arrive(&sc.empty_bar[prev_s]);
+    }
+    prev_s = s;
+  }
+  if (nstage) {
+    ptx::bulk_wait_group_read0();
+    epi_bar();
+    if (etid == 0) ptx::mbar_arrive(&sc.empty_bar[prev_s]);
+  }
+  prof_mark(p, sc, etid, 53);
+  ptx::bulk_wait_group0();  // this thread's copies are written
+  epi_bar();
+  prof_mark(p, sc, etid, 54);
+  // The rows of this task have landed: count them per expert (and batch) on the owner and publish
+  // the FFN1 tiles of every batch this completes.  One fence per signalling thread orders the rows
+  // and sidebands (written by other threads of the group, before the barrier) first; it is the only
+  // system-scope fence of the task, issued when nothing else of this worker is in flight.
+  if (etid < p.E && !sc.abort) {
+    const uint32_t cnt = sc.cnt[etid];
+    if (cnt) {
+      const int owner = etid / p.El, le = etid - owner * p.El;
+      if (S && owner != p.rank) {
+        fence_acqrel<true>();
+        rows_landed<true>(p, sc.batch_mt, owner, (uint32_t)le, sc.base[etid], cnt);
+      } else {
+        fence_acqrel<false>();
+        rows_landed<false>(p, sc.batch_mt, owner, (uint32_t)le, sc.base[etid], cnt);
+      }
+    }
+  }
+  epi_bar();
+  prof_mark(p, sc, etid, 55);
   if (ewarp == 0) {
-    ptx::bulk_wait_group0();  // this lane's rows are written
-    __syncwarp();
+    if (lane == 0) atomicSub(&p.peers[p.rank].ctl->disp_active, 1u);
+    count_gated<S>(p, sc, lane, nt - sc.n_flagged);
   }
-  ptx::fence_proxy_async();  // packed rows are read by TMA
-  epi_bar();
-  if (etid == 0) {
-    fence_acqrel<S>();
-    const uint32_t prev = atom_add<S>(&op.landed[le], count);
-    // Complete?  The row count of the expert is only final once every rank has gated; before that
-    // the second GATED round of the owner will look at the expert again.  (Sequentially consistent
-    // fences here and there: of this check and that look, at least one sees the other's update.)
-    fence_sc<S>();
-    const uint32_t total = ld_relaxed<S>(&op.expert_cnt[le]);
-    const bool final_cnt = ld_acquire<S>(&op.ctl->ranks_gated) == (uint32_t)p.world;
-    sc.flag = (final_cnt && prev + count == total) ? (int)total : 0;
-  }
-  epi_bar();
-  if (sc.flag) publish_expert_tiles<S>(p, sc, etid, op, (uint32_t)le, (uint32_t)sc.flag);
-  if (etid == 32) {
-    // this piece is done: the next entry of this rank's pack list may go out
-    FdmoeCtl* myctl = p.peers[p.rank].ctl;
-    const uint32_t nxt = atomicAdd(&myctl->pack_cursor, 1u);
-    if (nxt < ld_relaxed<false>(&myctl->pack_total)) {
-      const uint4 t = ld_cg_u4(reinterpret_cast<const uint4*>(p.pack_list) + nxt);
-      queue_push<false>(p, p.peers[p.rank], 1u, [&](uint32_t, uint32_t& a, uint32_t& b, uint32_t& c) {
-        a = t.x;
-        b = t.y;
-        c = t.z;
-      });
-    }
-  }
-  epi_bar();  // sc.flag / sc.q_t0 may be rewritten by the next task only after everyone has read them
   return true;
 }
 
 // ================================================================== GATEFIX
 // Up to two tokens whose leading tensor-core logits were nearly tied: all E
 // logits are recomputed with fp32 FMAs in the reference's order (128 threads per
-// token, one expert each), then top-k, softmax, row reservation and send-list
-// entries, i.e. everything GATE does for the other tokens.
+// token, one expert each), then top-k, softmax, row reservation and the dispatch
+// of the token's K rows, i.e. everything GATE does for the other tokens.
 template <bool S>
 __device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uint8_t* stage, uint32_t& stage_it,
                                           int etid, int ewarp, int lane, uint32_t tok_a, uint32_t tok_b) {
@@ -919,13 +950,17 @@ __device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uin
     if (lane < K) {
       const float w = ex / sum;
       const int owner = myi / p.El, le = myi - owner * p.El;
-      const uint32_t pos = atom_add<S>(&p.peers[owner].expert_cnt[le], 1u);
+      uint32_t pos;
+      if (S && owner != p.rank)
+        pos = atom_add<true>(&p.peers[owner].expert_cnt[le], 1u);
+      else
+        pos = atom_add<false>(&p.peers[owner].expert_cnt[le], 1u);
       sc.fix_dst[half][lane] = make_uint2(0xffffffffu, 0u);
       if (pos >= (uint32_t)p.cap_rows) {
         raise_error(p, sc, FDMOE_ERR_ROW_OVERFLOW, (uint32_t)myi);
       } else {
         const size_t rowg = (size_t)le * p.cap_rows + pos;
-        sc.fix_dst[half][lane] = make_uint2((uint32_t)myi, (uint32_t)rowg);  // this task sends the row itself (below)
+        sc.fix_dst[half][lane] = make_uint2((uint32_t)myi, pos);
         p.topk_idx[(size_t)tok * K + lane] = myi;
         p.topk_w[(size_t)tok * K + lane] = w;
         *reinterpret_cast<uint4*>(&p.peers[owner].meta[rowg]) =
@@ -935,157 +970,101 @@ __device__ __noinline__ bool gatefix_task(const FdmoeParams& p, SmemCtl& sc, uin
   }
   epi_bar();
   prof_mark(p, sc, etid, 32);
-  // The token row (still in shared memory) goes to its K rows in the owners' expert buffers: these few
-  // rows do not pass through PACK tasks.  Their landing counts as gated only below, so no expert can be
-  // found complete with its count believed final before these rows are there; the second GATED round
-  // looks at the experts they completed.
+  // The token row (still in shared memory) goes to its K rows in the owners' expert buffers.
   if (live) {
     for (int k = 0; k < K; ++k) {
       const uint2 d = sc.fix_dst[half][k];
       if (d.x == 0xffffffffu) continue;
-      const int owner = (int)d.x / p.El;
-      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.peers[owner].packed) + (size_t)d.y * H);
+      const int owner = (int)d.x / p.El, le = (int)d.x - owner * p.El;
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.peers[owner].packed) +
+                                            ((size_t)le * p.cap_rows + d.y) * H);
       for (int v = e; v < H / 8; v += 128) dst[v] = sc.xrow[half][v];
     }
-    fence_acqrel<S>();
     ptx::fence_proxy_async();  // packed rows are read by TMA
   }
   epi_bar();
+  // the rows have been stored (by all threads, before the barrier): count them on their owners
   if (live && e < K) {
     const uint2 d = sc.fix_dst[half][e];
     if (d.x != 0xffffffffu) {
       const int owner = (int)d.x / p.El, le = (int)d.x - owner * p.El;
-      fence_acqrel<S>();
-      atom_add<S>(&p.peers[owner].landed[le], 1u);
+      if (S && owner != p.rank) {
+        fence_acqrel<true>();
+        rows_landed<true>(p, sc.batch_mt, owner, (uint32_t)le, d.y, 1u);
+      } else {
+        fence_acqrel<false>();
+        rows_landed<false>(p, sc.batch_mt, owner, (uint32_t)le, d.y, 1u);
+      }
     }
   }
   epi_bar();
-  if (etid == 0) count_gated<S>(p, sc, (tok_b != 0xffffffffu) ? 2u : 1u);
+  if (ewarp == 0) count_gated<S>(p, sc, lane, (tok_b != 0xffffffffu) ? 2u : 1u);
   return true;
 }
 
-// ============================================================ GATED and FFN
-// GATED, first round, as soon as this rank's GATE tiles are done: lays out this rank's PACK tasks
-// (pieces of FDMOE_PACK_ROWS rows of its send lists: the rows of all tokens but the nearly tied
-// ones, which their GATEFIX tasks send themselves) in sending order and publishes the first
-// pack_window of them; every PACK task that finishes publishes the next one, so that packing,
-// whose pace is set by memory writes or by NVLink, shares the workers with the GATEFIX tasks and
-// with the FFN1 tiles of experts that have already landed.  Sending order: step i goes to local
-// expert i / world of rank (rank + 1 + i) % world, so that at every step the ranks send to
-// different owners and the experts of all ranks complete one after the other.
-// Second round, once every rank has gated (row counts are final): the number of m-tiles this
-// rank will process (termination), and a look at this rank's experts for any that landed
-// completely before their count was known to be final.
+// ==================================================================== GATED
+// Every rank has gated and all rows have landed: the row counts of this rank's experts are final.
+// Sets the number of m-tiles this rank will process (termination) and publishes, expert by expert,
+// the FFN1 tiles of every m-tile that no sender has published as part of a complete batch: with
+// batches of B m-tiles, an expert with F full m-tiles has had its first (F / B) * B published.
 template <bool S>
-__device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int etid, bool first_round) {
+__device__ __noinline__ void gated_task(const FdmoeParams& p, SmemCtl& sc, int etid) {
   const FdmoePeer& me = p.peers[p.rank];
   const int lane = etid & 31, w = etid >> 5;
-  // (the task was taken from the queue with an acquire load ordered after the events it stands for)
-  uint32_t ntile = 0, npack = 0, ecnt = 0, lcnt = 0;
-  const int e_send = (etid < p.E) ? ((p.rank + 1 + etid) % p.world) * p.El + etid / p.world : 0;
-  if (!first_round && etid < p.El) {
+  const uint32_t B = sc.batch_mt;
+  const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
+  // (the caller observed every rank's gating count with an atomic or took this task from the queue
+  // with an acquire load; order this thread's reads after that)
+  fence_acqrel<S>();
+  uint32_t lcnt = 0, ntile = 0, first = 0;
+  if (etid < p.El) {
     lcnt = ld_relaxed<S>(&me.expert_cnt[etid]);
     ntile = (lcnt + 127u) / 128u;
+    first = ((lcnt / 128u) / B) * B;
   }
-  if (first_round && etid < p.E) {
-    ecnt = __ldcg(&p.send_cnt[e_send]);
-    npack = (ecnt + FDMOE_PACK_ROWS - 1) / FDMOE_PACK_ROWS;
-  }
-  uint32_t inc_pack = npack, inc_tile = ntile;
+  const uint32_t mytasks = (ntile - first) * nt1;
+  uint32_t inc = mytasks, inc_tile = ntile;
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
-    const uint32_t a = __shfl_up_sync(0xffffffffu, inc_pack, off);
+    const uint32_t a = __shfl_up_sync(0xffffffffu, inc, off);
     const uint32_t b = __shfl_up_sync(0xffffffffu, inc_tile, off);
     if (lane >= off) {
-      inc_pack += a;
+      inc += a;
       inc_tile += b;
     }
   }
   if (lane == 31 && w < 4) {
-    sc.pre[w] = inc_pack;
+    sc.pre[w] = inc;
     sc.pre[8 + w] = inc_tile;
   }
   epi_bar();
-  uint32_t off_pack = 0, total = 0, mt = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    if (i < w) off_pack += sc.pre[i];
-    total += sc.pre[i];
-    mt += sc.pre[8 + i];
-  }
-  if (first_round) {
-    const uint32_t window = min(total, (uint32_t)p.pack_window);
-    if (etid == 0) {
-      sc.q_t0 = window ? atom_add<false>(&me.ctl->q_head, window) : 0u;
-      st_relaxed<false>(&me.ctl->pack_total, total);
-      st_relaxed<false>(&me.ctl->pack_cursor, window);
-    }
-    // the tasks in sending order: entries [first, first + count) of the expert's send list
-    uint4* plist = reinterpret_cast<uint4*>(p.pack_list);
-    const uint32_t firstslot = off_pack + inc_pack - npack;  // exclusive prefix in sending order
-    for (uint32_t r = 0; r < npack; ++r)
-      plist[firstslot + r] = make_uint4(task_word(FDMOE_TASK_PACK, (uint32_t)e_send, 0u), r * FDMOE_PACK_ROWS,
-                                        min((uint32_t)FDMOE_PACK_ROWS, ecnt - r * FDMOE_PACK_ROWS), 0u);
-    epi_bar();
-    const uint32_t t0 = sc.q_t0;
-    bool any = false;
-    for (uint32_t idx = (uint32_t)etid; idx < window; idx += kEpiThreads) {
-      const uint4 t = ld_cg_u4(&plist[idx]);
-      FdmoeSlot* sl = &me.slots[(t0 + idx) & (uint32_t)p.queue_mask];
-      sl->a = t.x;
-      sl->b = t.y;
-      sl->c = t.z;
-      any = true;
-    }
-    // one fence orders every payload (and the list, the cursor and the total) before every sequence word below
-    if (any || etid == 0) fence_acqrel<false>();
-    for (uint32_t idx = (uint32_t)etid; idx < window; idx += kEpiThreads)
-      st_relaxed<false>(&me.slots[(t0 + idx) & (uint32_t)p.queue_mask].seq, t0 + idx + 1u);
-    epi_bar();
-    if (etid == 0 && p.pack_early) second_round_ready<S>(p, &sc, p.rank, 1u);
-    return;
-  }
-  if (etid == 0) st_relaxed<false>(&me.ctl->mtiles_total, mt);
-  // Experts of this rank whose rows had all landed while their count was not yet known to be final:
-  // nobody has published their tiles.  (Fence: see pack_task.)  Every thread looks at one expert and
-  // claims it; the tasks of all claimed experts are published in one batch.
-  fence_sc<S>();
-  const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1);
-  const bool cand = etid < p.El && lcnt != 0u && ld_relaxed<S>(&me.landed[etid]) == lcnt &&
-                    atom_exch<S>(&me.published[etid], 1u) == 0u;
-  const uint32_t mytasks = cand ? ((lcnt + 127u) / 128u) * nt1 : 0u;
-  uint32_t inc = mytasks;
-#pragma unroll
-  for (int off = 1; off < 32; off <<= 1) {
-    const uint32_t a = __shfl_up_sync(0xffffffffu, inc, off);
-    if (lane >= off) inc += a;
-  }
-  if (lane == 31 && w < 4) sc.pre[w] = inc;
-  epi_bar();
-  uint32_t before = 0, all = 0;
+  uint32_t before = 0, all = 0, mt = 0;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     if (i < w) before += sc.pre[i];
     all += sc.pre[i];
+    mt += sc.pre[8 + i];
   }
-  if (etid == 0 && all) {
-    fence_acqrel<S>();
-    sc.q_t0 = atom_add<false>(&me.ctl->q_head, all);
+  if (etid == 0) {
+    st_relaxed<false>(&me.ctl->mtiles_total, mt);
+    sc.q_t0 = all ? atom_add<false>(&me.ctl->q[1].head, all) : 0u;
   }
   epi_bar();
   if (mytasks) {
     const uint32_t t1 = sc.q_t0 + before + inc - mytasks;
     const uint32_t full = lcnt / 128u, rem = lcnt % 128u;
+    FdmoeSlot* slots = me.slots[1];
     for (uint32_t idx = 0; idx < mytasks; ++idx) {
-      const uint32_t jt = idx / nt1, n = idx - jt * nt1;
-      FdmoeSlot* sl = &me.slots[(t1 + idx) & (uint32_t)p.queue_mask];
+      const uint32_t jt = first + idx / nt1, n = idx % nt1;
+      FdmoeSlot* sl = &slots[(t1 + idx) & (uint32_t)p.queue_mask];
       sl->a = task_word(FDMOE_TASK_FFN1, (uint32_t)etid, n);
       sl->b = jt;
       sl->c = (jt < full) ? 128u : rem;
     }
     fence_acqrel<false>();
     for (uint32_t idx = 0; idx < mytasks; ++idx)
-      st_relaxed<false>(&me.slots[(t1 + idx) & (uint32_t)p.queue_mask].seq, t1 + idx + 1u);
+      st_relaxed<false>(&slots[(t1 + idx) & (uint32_t)p.queue_mask].seq, t1 + idx + 1u);
+    atom_add<false>(&me.ctl->q[1].avail, mytasks);
   }
   epi_bar();
   if (etid == 0) {
@@ -1131,7 +1110,7 @@ __device__ __forceinline__ void ffn1_epilogue(const FdmoeParams& p, SmemCtl& sc,
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const uint32_t r = q * 32 + (lane >> 2) + 8 * i;
-    ok[i] = r < rows && !(p.debug_flags & 1);
+    ok[i] = r < rows;
     dst[i] = reinterpret_cast<uint8_t*>(reinterpret_cast<bf16*>(p.act) +
                                         ((size_t)e * p.cap_rows + (size_t)j * 128 + r) * p.I +
                                         n * FDMOE_TILE_N1 + h * 64);
@@ -1156,18 +1135,20 @@ __device__ __forceinline__ void ffn1_epilogue(const FdmoeParams& p, SmemCtl& sc,
 }
 
 // FFN2 epilogue: y[token, slot, n*256 + c] = D[row, c] * routing weight, stored
-// on the token's home rank.
-__device__ __forceinline__ void ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, int q, int h,
+// on the token's home rank.  Returns whether this thread's row went to another GPU.
+__device__ __forceinline__ bool ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc, uint32_t taddr, int q, int h,
                                               int lane, int ewarp, uint32_t e, uint32_t j, uint32_t n,
                                               uint32_t rows) {
   uint8_t* st = sc.store_stage[ewarp];
   const uint32_t row = q * 32 + lane;
   float wgt = 0.f;
   unsigned long long myptr = 0ull;
+  bool remote = false;
   if (row < rows) {
     const uint4 mraw = ld_cg_u4(&p.peers[p.rank].meta[(size_t)e * p.cap_rows + (size_t)j * 128 + row]);
     const int token = (int)mraw.x, home = (int)mraw.y >> 8, slot = (int)mraw.y & 0xff;
     wgt = __uint_as_float(mraw.z);
+    remote = home != p.rank;
     myptr = reinterpret_cast<unsigned long long>(reinterpret_cast<bf16*>(p.peers[home].ystage) +
                                                  ((size_t)token * p.K + slot) * p.H + n * FDMOE_TILE_N2 + h * 128);
   }
@@ -1177,7 +1158,7 @@ __device__ __forceinline__ void ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc,
   for (int i = 0; i < 4; ++i) {
     const unsigned long long pp = __shfl_sync(0xffffffffu, myptr, (lane >> 2) + 8 * i);
     dst[i] = reinterpret_cast<uint8_t*>(pp);
-    ok[i] = pp != 0ull && !(p.debug_flags & 1);
+    ok[i] = pp != 0ull;
   }
   const uint32_t tbase = taddr + ((uint32_t)(q * 32) << 16) + h * 128;
 #pragma unroll
@@ -1191,6 +1172,7 @@ __device__ __forceinline__ void ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc,
     uint8_t* d2[4] = {dst[0] + c * 64, dst[1] + c * 64, dst[2] + c * 64, dst[3] + c * 64};
     store_chunk_coalesced(st, lane, o, d2, ok);
   }
+  return remote;
 }
 
 // COMBINE streams the K weighted rows of each token of a group through the
@@ -1202,6 +1184,28 @@ constexpr int kCombineCols = 2048;
 // (H is a multiple of 256, so the number of k-blocks is even), one otherwise.
 __device__ __forceinline__ uint32_t gate_kblocks_per_stage(bool is_gate, int gate_rows) {
   return (is_gate && gate_rows <= 64) ? 2u : 1u;
+}
+
+// Pipeline stages a DISPATCH task of `nt` tokens takes (whole token rows per stage).
+__device__ __forceinline__ uint32_t dispatch_stages(const FdmoeParams& p, uint32_t nt) {
+  const uint32_t rps = dispatch_rows_per_stage(p.H);
+  return (nt + rps - 1u) / rps;
+}
+
+// Barrier over the 256 epilogue threads that also ORs a predicate.
+__device__ __forceinline__ bool epi_vote_any(bool v) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.or.pred q, 1, 256, p;\n\t"
+      "selp.b32 %0, 1, 0, q;\n\t"
+      "}\n"
+      : "=r"(r)
+      : "r"((uint32_t)v)
+      : "memory");
+  return r != 0;
 }
 
 template <bool S>
@@ -1240,7 +1244,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
     sc.flag = 0;
     sc.prof_n = 0;
     ptx::fence_mbar_init();
-    st_relaxed<S>(&ctl->tokens_launch, (uint32_t)p.T);
+    st_relaxed<false>(&ctl->tokens_launch, (uint32_t)p.T);
   }
   {
     static_assert(sizeof(FdmoeParams) % 16 == 0, "parameter block is copied in 16-byte pieces");
@@ -1265,46 +1269,42 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = sc.tmem_base;
 
-  // ---- multi-GPU: announce this launch to the peers and wait (bounded) until
-  // every peer has entered the same launch, i.e. has reset its counters.
+  // ---- multi-GPU: announce this launch (and this rank's token count) to the peers and wait,
+  // with a budget of its own, until every peer has entered the same launch, i.e. has reset its
+  // counters.  A peer that is already one launch further has passed this one.
   if (S && p.world > 1) {
     if (blockIdx.x == 0 && tid < p.world && tid != p.rank) {
-      fence_acqrel<true>();
-      ptx::st_release_sys(&p.peers[tid].ctl->ready[p.rank], p.epoch);
+      FdmoeCtl* pc = p.peers[tid].ctl;
+      st_relaxed<true>(&pc->tokens_of[p.epoch & 1u][p.rank], (uint32_t)p.T);
+      ptx::st_release_sys(&pc->ready[p.rank], p.epoch);
     }
     if (tid < p.world && tid != p.rank) {
       const uint64_t t0 = ptx::globaltimer_ns();
-      while (ptx::ld_acquire_sys(&ctl->ready[tid]) != p.epoch) {
+      uint32_t spins = 0;
+      while ((int32_t)(ptx::ld_acquire_sys(&ctl->ready[tid]) - p.epoch) < 0) {
         if (sc.abort || ld_relaxed<true>(&ctl->closed) == 2u) break;
-        if (ptx::globaltimer_ns() - t0 > p.timeout_ns) {
+        if (ptx::globaltimer_ns() - t0 > p.peer_timeout_ns) {
           raise_error(p, sc, FDMOE_ERR_TIMEOUT_PEER, (uint32_t)tid);
           break;
         }
-        __nanosleep(200);
+        __nanosleep(++spins < 1000u ? 200 : 2000);
       }
     }
     __syncthreads();
   }
-
-  // ---- seed the queue: every CTA publishes its share of the GATE tasks (tile b, b + grid, ...),
-  // so that all tiles are available at once.  Nothing to gate: the rank's "gate phase" is
-  // finished at once (it may still serve its peers).
-  if (p.mode != 2 && !sc.abort && tid == 0) {
-    const uint32_t n_tiles = (p.T > 0 && p.gate_rows > 0) ? (uint32_t)((p.T + p.gate_rows - 1) / p.gate_rows) : 0u;
-    if (n_tiles == 0) {
-      if (blockIdx.x == 0) {
-        second_round_ready<S>(p, nullptr, p.rank, 1u);  // no first round to wait for
-        gating_finished<S>(p, nullptr);
-      }
-    } else if (blockIdx.x < n_tiles) {
-      const uint32_t mine = (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
-      queue_push<false>(p, me, mine, [](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
-        a = FDMOE_TASK_GATE;
-        b = blockIdx.x + i * gridDim.x;
-        c = 0;
-      });
-    }
+  if (tid == 0) {
+    uint32_t all = 0u;
+    for (int r = 0; r < p.world; ++r) all += tokens_of_rank(p, r);
+    sc.tokens_all = all;
+    sc.batch_mt = batch_mt_of(p, all);
   }
+  __syncthreads();
+
+  // ---- GATE tiles are claimed from a counter by whichever worker is free.  Nothing to gate:
+  // the rank's "gate phase" is finished at once (it may still serve its peers).
+  const uint32_t gate_tiles =
+      (p.mode != 2 && p.T > 0 && p.gate_rows > 0) ? (uint32_t)((p.T + p.gate_rows - 1) / p.gate_rows) : 0u;
+  if (p.mode != 2 && gate_tiles == 0u && blockIdx.x == 0 && warp == 0 && !sc.abort) gating_finished<S>(p, nullptr, lane);
 
   // =============================== worker loop
   const uint32_t nt1 = (uint32_t)(p.I / FDMOE_TILE_N1), nt2 = (uint32_t)(p.H / FDMOE_TILE_N2);
@@ -1312,23 +1312,19 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
 
   if (warp == kWarpSched) {
     if (lane == 0) {
-      uint32_t ticket = 0;
-      bool has_ticket = false;
       for (uint32_t it = 0;; ++it) {
         const uint32_t r = it % kRing, ph = (it / kRing) & 1u;
-        if (!wait_bar(p, sc, &sc.ring_empty[r], ph ^ 1u, FDMOE_ERR_TIMEOUT_RING)) {
-          // The ring may be wedged: hand out EXIT through every slot that is free.
-          break;
-        }
-        const FdmoeSlot t = queue_pop<S>(p, sc, ticket, has_ticket);
+        if (!wait_bar(p, sc, &sc.ring_empty[r], ph ^ 1u, FDMOE_ERR_TIMEOUT_RING)) break;
+        const FdmoeSlot t = next_task<S>(p, sc, gate_tiles);
         sc.ring[r] = t;
         ptx::mbar_arrive(&sc.ring_full[r]);
         const uint32_t kind = t.a & 0xffu;
         if (kind == FDMOE_TASK_EXIT) break;
-        if (kind != FDMOE_TASK_FFN1 && kind != FDMOE_TASK_FFN2 && kind != FDMOE_TASK_COMBINE && kind != FDMOE_TASK_PACK) {
-          // Only tile tasks (and COMBINE / PACK, whose rows travel as bulk copies) profit from being queued behind one another (their loads and
-          // MMAs run ahead of the epilogue).  Behind a long task of another kind a claimed
-          // ticket would just sit here while other workers idle: wait until it is done.
+        if (kind != FDMOE_TASK_FFN1 && kind != FDMOE_TASK_FFN2 && kind != FDMOE_TASK_COMBINE) {
+          // Only tile tasks (and COMBINE, whose rows travel as bulk copies) profit from being queued
+          // behind one another (their loads and MMAs run ahead of the epilogue).  Behind a long task
+          // of another kind a claimed task would just sit here while other workers idle: wait until
+          // it is done.
           if (!wait_bar(p, sc, &sc.ring_empty[r], ph, FDMOE_ERR_TIMEOUT_RING)) break;
         }
       }
@@ -1361,10 +1357,6 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
             if (!ok) break;
             uint8_t* sa = stage + s * kStageBytes;
             uint8_t* sb = sa + kStageA;
-            if ((p.debug_flags & 8) && !gt) {  // timing experiment: tiles computed from stale operands
-              ptx::mbar_arrive(&sc.full_bar[s]);
-              continue;
-            }
             ptx::mbar_expect_tx(&sc.full_bar[s], gt ? gk * gate_bytes : (uint32_t)kStageBytes);
             const int32_t kx = (int32_t)(kb * FDMOE_TILE_K);
             if (gt) {
@@ -1384,6 +1376,21 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
             }
           }
           if (!ok) break;
+        } else if (kind == FDMOE_TASK_DISPATCH) {
+          // the tokens' rows: contiguous in the token matrix, one bulk copy per stage
+          const uint32_t rowb = (uint32_t)p.H * 2u, rps = dispatch_rows_per_stage(p.H);
+          const uint32_t nt = t.c;
+          const uint8_t* xb = reinterpret_cast<const uint8_t*>(p.x) + (size_t)t.b * rowb;
+          bool ok = true;
+          for (uint32_t r0 = 0; r0 < nt && ok; r0 += rps, ++stage_it) {
+            const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
+            ok = wait_bar(p, sc, &sc.empty_bar[s], sph ^ 1u, FDMOE_ERR_TIMEOUT_STAGE);
+            if (!ok) break;
+            const uint32_t bytes = min(rps, nt - r0) * rowb;
+            ptx::mbar_expect_tx(&sc.full_bar[s], bytes);
+            ptx::bulk_load_1d(stage + s * kStageBytes, xb + (size_t)r0 * rowb, bytes, &sc.full_bar[s]);
+          }
+          if (!ok) break;
         } else if (kind == FDMOE_TASK_GATEFIX) {
           bool ok = true;
           for (uint32_t kb = 0; kb < nkb1; kb += kFixBlocks, ++stage_it) {
@@ -1397,9 +1404,6 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
               ptx::tma_load_2d(stage + s * kStageBytes + i * kStageA, &p.tm_gate, &sc.full_bar[s],
                                (int32_t)((kb + i) * FDMOE_TILE_K), 0);
           }
-          if (!ok) break;
-        } else if (kind == FDMOE_TASK_PACK) {
-          const bool ok = pack_loads(sc.params, sc, stage, stage_it, (t.a >> 8) & 0xfffu, t.b, t.c);
           if (!ok) break;
         } else if (kind == FDMOE_TASK_COMBINE) {
           const int t_begin = (int)t.b, t_end = t_begin + (int)t.c;
@@ -1436,6 +1440,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         const FdmoeSlot t = sc.ring[r];
         const uint32_t kind = t.a & 0xffu;
         if (kind == FDMOE_TASK_EXIT) break;
+        bool ok = true;
         if (kind == FDMOE_TASK_FFN1 || kind == FDMOE_TASK_FFN2 || kind == FDMOE_TASK_GATE) {
           const uint32_t nkb = (kind == FDMOE_TASK_FFN2) ? nkb2 : nkb1;
           const uint32_t idesc = (kind == FDMOE_TASK_GATE) ? idesc128 : idesc256;
@@ -1445,7 +1450,6 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           ptx::tcgen05_fence_after();
           const uint32_t d_tmem = tmem_base + acc * kAccCols;
           const uint32_t gk = gate_kblocks_per_stage(kind == FDMOE_TASK_GATE, p.gate_rows);
-          bool ok = true;
           for (uint32_t kb = 0; kb < nkb; kb += gk, ++stage_it) {
             const uint32_t s = stage_it % kStages, sph = (stage_it / kStages) & 1u;
             ok = wait_bar(p, sc, &sc.full_bar[s], sph, FDMOE_ERR_TIMEOUT_STAGE);
@@ -1466,15 +1470,15 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           }
           if (!ok) break;
           ptx::umma_commit(&sc.tmem_full[acc]);
-        } else if (kind == FDMOE_TASK_GATEFIX || kind == FDMOE_TASK_COMBINE || kind == FDMOE_TASK_PACK) {
-          // The stages of these tasks are consumed by the epilogue warps.  This warp must not
-          // run ahead of them: a stage barrier only tells phases apart by parity, so a waiter
-          // more than one phase ahead would take an old completion for its own.  Wait until
-          // the epilogue has finished the task, then step over its stages.
+        }
+        if (kind == FDMOE_TASK_DISPATCH || kind == FDMOE_TASK_GATEFIX || kind == FDMOE_TASK_COMBINE) {
+          // Stages of these tasks are consumed
+          // by the epilogue warps.  This warp must not run ahead of them: a stage barrier only tells
+          // phases apart by parity, so a waiter more than one phase ahead would take an old completion
+          // for its own.  Wait until the epilogue has finished the task, then step over its stages.
           ++skips;
           const uint64_t t0w = ptx::globaltimer_ns();
           uint32_t spins = 0;
-          bool ok = true;
           while (sc.skip_done < skips) {
             if ((++spins & 63u) == 0u) {
               if (sc.abort) { ok = false; break; }
@@ -1487,14 +1491,12 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
             }
           }
           if (!ok) break;
-          if (kind == FDMOE_TASK_GATEFIX) {
+          if (kind == FDMOE_TASK_DISPATCH) {
+            stage_it += dispatch_stages(p, t.c);
+          } else if (kind == FDMOE_TASK_GATEFIX) {
             stage_it += (nkb1 + kFixBlocks - 1) / kFixBlocks;
-          } else if (kind == FDMOE_TASK_PACK) {
-            const uint32_t rps = pack_rows_per_stage(p.H);
-            stage_it += (t.c + rps - 1u) / rps;
           } else {
-            const int t_begin = (int)t.b, t_end = t_begin + (int)t.c;
-            stage_it += (uint32_t)((t_end - t_begin) * ((p.H + kCombineCols - 1) / kCombineCols));
+            stage_it += t.c * (uint32_t)((p.H + kCombineCols - 1) / kCombineCols);
           }
         }
         ptx::mbar_arrive(&sc.ring_empty[r]);
@@ -1524,8 +1526,8 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         if (p.prof && etid == 0) pt1 = prof_now();
         ptx::tcgen05_fence_after();
         gate_epilogue<S>(sc.params, sc, tmem_base + acc * kAccCols, &sc.tmem_empty[acc], q, h, lane, etid, ewarp, j);
-      } else if (kind == FDMOE_TASK_PACK) {
-        if (!pack_task<S>(sc.params, sc, stage, stage_it, etid, ewarp, lane, e, j, rows)) break;
+      } else if (kind == FDMOE_TASK_DISPATCH) {
+        if (!dispatch_task<S>(sc.params, sc, stage, stage_it, etid, ewarp, lane, j, rows)) break;
         if (etid == 0) {
           __threadfence_block();
           sc.skip_done = sc.skip_done + 1u;
@@ -1544,10 +1546,11 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         if (p.prof && etid == 0) pt1 = prof_now();
         ptx::tcgen05_fence_after();
         const uint32_t taddr = tmem_base + acc * kAccCols;
+        bool remote = false;
         if (kind == FDMOE_TASK_FFN1)
           ffn1_epilogue(p, sc, taddr, q, h, lane, ewarp, e, j, n, rows);
         else
-          ffn2_epilogue(p, sc, taddr, q, h, lane, ewarp, e, j, n, rows);
+          remote = ffn2_epilogue(p, sc, taddr, q, h, lane, ewarp, e, j, n, rows);
         ptx::tcgen05_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&sc.tmem_empty[acc]);
@@ -1557,12 +1560,14 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         // the notifications of the home ranks are done by the completion warp, off
         // the epilogue's critical path.
         // activations are read by TMA in FFN2, weighted rows by bulk copies in COMBINE
-        if (!(p.debug_flags & 4)) ptx::fence_proxy_async();
-        epi_bar();
+        ptx::fence_proxy_async();
+        const bool any_remote = S ? epi_vote_any(remote) : (epi_bar(), false);
         if (etid == 0 && p.mode != 2) {
           const uint32_t d = done_it % kDone, dph = (done_it / kDone) & 1u;
           if (wait_bar(p, sc, &sc.done_empty[d], dph ^ 1u, FDMOE_ERR_TIMEOUT_RING)) {
-            sc.done_ring[d] = t;
+            FdmoeSlot dt = t;
+            dt.seq = any_remote ? 1u : 0u;  // rows of this tile went to another GPU
+            sc.done_ring[d] = dt;
             ptx::mbar_arrive(&sc.done_full[d]);
           }
         }
@@ -1615,8 +1620,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           maybe_close(p);
         }
       } else if (kind == FDMOE_TASK_GATED) {
-        if (j == 0u && !p.pack_early) gated_task<S>(sc.params, sc, etid, true);  // packing was held back until now
-        gated_task<S>(sc.params, sc, etid, j == 1u);
+        gated_task<S>(sc.params, sc, etid);
       } else if (kind == FDMOE_TASK_TESTA || kind == FDMOE_TASK_TESTB) {
         // task-system self test: two dependent stages over a 256-element chunk
         int* ptr = p.test_buf + (size_t)j * kEpiThreads + etid;
@@ -1625,7 +1629,8 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           epi_bar();
           if (etid == 0) {
             fence_acqrel<false>();
-            queue_push<false>(p, me, 1u, [&](uint32_t, uint32_t& a, uint32_t& b, uint32_t& c) {
+            // (alternating queues, so that the test exercises both)
+            queue_push<false>(p, me, (int)(j & 1u), 1u, [&](uint32_t, uint32_t& a, uint32_t& b, uint32_t& c) {
               a = FDMOE_TASK_TESTB;
               b = j;
               c = 0;
@@ -1637,15 +1642,14 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       } else {
         if (etid == 0) raise_error(p, sc, FDMOE_ERR_BAD_TASK, t.a);
       }
-      if (kind == FDMOE_TASK_GATE || kind == FDMOE_TASK_GATEFIX || kind == FDMOE_TASK_GATED) {
-        // the task may have found this rank's second GATED round due: run it here and now
+      if (kind == FDMOE_TASK_DISPATCH || kind == FDMOE_TASK_GATEFIX) {
+        // the task may have found this rank's GATED round due: run it here and now
         epi_bar();
         const bool r2 = sc.run_round2 != 0u;
         epi_bar();
         if (r2) {
           if (etid == 0) sc.run_round2 = 0u;
-          if (!p.pack_early) gated_task<S>(sc.params, sc, etid, true);
-          gated_task<S>(sc.params, sc, etid, false);
+          gated_task<S>(sc.params, sc, etid);
         }
       }
       if (p.mode == 2) {
@@ -1669,110 +1673,155 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       }
     }
   } else if (warp == kWarpTmem && p.mode != 2) {
-    // ---- completion warp: per finished tile, count it and publish what it unblocks
-    for (uint32_t it = 0;; ++it) {
-      const uint32_t d = it % kDone, dph = (it / kDone) & 1u;
+    // ---- completion warp: per finished tile, count it and publish what it unblocks.  It takes
+    // every entry that is ready at once and pays one fence for all of them.
+    const uint32_t G = (uint32_t)p.combine_group;
+    uint32_t it = 0;
+    for (bool running = true; running;) {
+      const uint32_t d0 = it % kDone, dph0 = (it / kDone) & 1u;
       int ok = 1;
+      uint32_t nready = 1u;
       if (lane == 0) {
         // This warp may legitimately idle for a whole launch, so its own budget is four
         // times the others': whoever actually stalls reports first.
         ok = 0;
         for (int tries = 0; tries < 4 && !ok && !sc.abort; ++tries)
-          ok = wait_idle(p, sc, &sc.done_full[d], dph) ? 1 : 0;
+          ok = wait_idle(p, sc, &sc.done_full[d0], dph0) ? 1 : 0;
         if (!ok && !sc.abort) raise_error(p, sc, FDMOE_ERR_TIMEOUT_RING, (blockIdx.x << 8) | 3u);
+        if (ok) {
+          while (nready < (uint32_t)kDone) {
+            const uint32_t i2 = it + nready;
+            if (!ptx::mbar_try_wait(&sc.done_full[i2 % kDone], (i2 / kDone) & 1u)) break;
+            ++nready;
+          }
+        }
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
-      const FdmoeSlot t = sc.done_ring[d];
-      const uint32_t kind = t.a & 0xffu;
-      if (kind == FDMOE_TASK_EXIT) break;
-      const uint32_t e = (t.a >> 8) & 0xfffu, j = t.b, rows = t.c;
-      if (kind == FDMOE_TASK_FFN1) {
-        if (lane == 0) {
-          if (!(p.debug_flags & 2)) fence_acqrel<false>();
-          const uint32_t prev = atomicAdd(&p.ffn1_done[(size_t)e * p.MT + j], 1u);
-          if (prev == nt1 - 1u) {
-            if (!(p.debug_flags & 2)) fence_acqrel<false>();
-            queue_push<false>(p, me, nt2, [&](uint32_t i, uint32_t& a, uint32_t& b, uint32_t& c) {
-              a = task_word(FDMOE_TASK_FFN2, e, i);
-              b = j;
-              c = rows;
-            });
-          }
+      nready = __shfl_sync(0xffffffffu, nready, 0);
+      // The stores of these tiles were made by the epilogue warps (handed over through the ring's
+      // barriers), the weighted rows of FFN2 tiles possibly on other GPUs: one fence of the widest
+      // scope needed makes them visible before anything counts them.
+      {
+        bool rem = false;
+        if ((uint32_t)lane < nready) {
+          const FdmoeSlot& tt = sc.done_ring[(it + (uint32_t)lane) % kDone];
+          rem = S && (tt.a & 0xffu) == FDMOE_TASK_FFN2 && tt.seq != 0u;
         }
-      } else {
-        int last = 0;
-        if (lane == 0) {
-          if (!(p.debug_flags & 2)) fence_acqrel<S>();
-          const uint32_t prev = atomicAdd(&p.ffn2_done[(size_t)e * p.MT + j], 1u);
-          if (!(p.debug_flags & 2)) fence_acqrel<S>();
-          last = prev == nt2 - 1u;
-        }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {
-          // every hidden-column tile of this m-tile is stored: tell each home rank how many
-          // of its rows that makes (one counter update per home rank and m-tile)
-          uint32_t cnt[FDMOE_MAX_WORLD];
-#pragma unroll
-          for (int w = 0; w < FDMOE_MAX_WORLD; ++w) cnt[w] = 0u;
-          if (p.world == 1) {
-            if (lane == 0) cnt[0] = rows;  // every row is this rank's own
-          } else {
-            for (uint32_t r = lane; r < rows; r += 32) {
-              const uint4 mraw = ld_cg_u4(&me.meta[(size_t)e * p.cap_rows + (size_t)j * 128 + r]);
-              const int home = (int)mraw.y >> 8;
-#pragma unroll
-              for (int w = 0; w < FDMOE_MAX_WORLD; ++w) cnt[w] += (home == w) ? 1u : 0u;
-            }
-          }
-          uint32_t mine = 0u;
-#pragma unroll
-          for (int w = 0; w < FDMOE_MAX_WORLD; ++w) {
-            const uint32_t c = __reduce_add_sync(0xffffffffu, cnt[w]);
-            if (lane == w) mine = c;
-          }
-          uint32_t th = 0u;
-          if (lane < p.world && mine) {
-            const FdmoePeer& hp = p.peers[lane];
-            fence_acqrel<S>();
-            const uint32_t prev = atom_add<S>(&hp.ctl->rows_arrived, mine);
-            const uint32_t tl = (lane == p.rank) ? (uint32_t)p.T : ld_relaxed<S>(&hp.ctl->tokens_launch);
-            if (prev + mine == tl * (uint32_t)p.K) th = tl;  // that home rank has all its rows
-          }
-          // ranks completed by this m-tile get their COMBINE tasks, published by the whole warp
-          uint32_t complete = __ballot_sync(0xffffffffu, th != 0u);
-          while (complete) {
-            const int home = __ffs(complete) - 1;
-            complete &= complete - 1u;
-            const uint32_t tl = __shfl_sync(0xffffffffu, th, home);
-            const FdmoePeer& hp = p.peers[home];
-            const uint32_t grp = combine_group_of((int)tl, (int)gridDim.x, p.combine_group);
-            const uint32_t ntask = (tl + grp - 1u) / grp;
-            uint32_t t0 = 0u;
-            if (lane == 0) {
-              fence_acqrel<S>();
-              t0 = atom_add<S>(&hp.ctl->q_head, ntask);
-            }
-            t0 = __shfl_sync(0xffffffffu, t0, 0);
-            for (uint32_t i = lane; i < ntask; i += 32) {
-              FdmoeSlot* sl = &hp.slots[(t0 + i) & (uint32_t)p.queue_mask];
-              sl->a = FDMOE_TASK_COMBINE;
-              sl->b = i * grp;
-              sl->c = min(grp, tl - i * grp);
-            }
-            fence_acqrel<S>();  // each lane: its payloads (and the arrival counts seen above) before its sequence words
-            for (uint32_t i = lane; i < ntask; i += 32)
-              st_relaxed<S>(&hp.slots[(t0 + i) & (uint32_t)p.queue_mask].seq, t0 + i + 1u);
-          }
-          __syncwarp();
-          if (lane == 0) {
-            atomicAdd(&ctl->mtiles_done, 1u);
-            maybe_close(p);
-          }
-        }
+        if (__any_sync(0xffffffffu, rem))
+          fence_acqrel<true>();
+        else
+          fence_acqrel<false>();
       }
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&sc.done_empty[d]);
+      for (uint32_t i = 0; i < nready; ++i, ++it) {
+        const uint32_t d = it % kDone;
+        const FdmoeSlot t = sc.done_ring[d];
+        const uint32_t kind = t.a & 0xffu;
+        if (kind == FDMOE_TASK_EXIT) {
+          running = false;
+          break;
+        }
+        const uint32_t e = (t.a >> 8) & 0xfffu, j = t.b, rows = t.c;
+        if (kind == FDMOE_TASK_FFN1) {
+          if (lane == 0) {
+            const uint32_t prev = atomicAdd(&p.ffn1_done[(size_t)e * p.MT + j], 1u);
+            if (prev == nt1 - 1u) {
+              // (the fence inside the push orders the other tiles' activations, observed through the
+              // counter, before the tasks)
+              queue_push<false>(p, me, 0, nt2, [&](uint32_t i3, uint32_t& a, uint32_t& b, uint32_t& c) {
+                a = task_word(FDMOE_TASK_FFN2, e, i3);
+                b = j;
+                c = rows;
+              });
+            }
+          }
+        } else {
+          int last = 0;
+          if (lane == 0) last = atomicAdd(&p.ffn2_done[(size_t)e * p.MT + j], 1u) == nt2 - 1u;
+          last = __shfl_sync(0xffffffffu, last, 0);
+          if (last) {
+            // Every hidden-column tile of this m-tile is stored (the other tiles' workers fenced before
+            // they counted): its rows are counted per COMBINE group on their home ranks, and whoever
+            // delivers the last row of a group publishes the group's COMBINE task there.  A lane owns up
+            // to four rows; it first counts them all, then publishes the groups it completed with one
+            // fence for the whole warp (the last m-tiles of a launch complete dozens of groups each).
+            fence_acqrel<false>();
+            uint32_t c_home[4], c_first[4], c_ntok[4], nc = 0u;
+#pragma unroll
+            for (uint32_t rr = 0; rr < 4u; ++rr) {
+              const uint32_t r = rr * 32u + (uint32_t)lane;
+              c_home[rr] = 0u;
+              c_first[rr] = 0u;
+              c_ntok[rr] = 0u;
+              if (r < rows) {
+                const uint4 mraw = ld_cg_u4(&me.meta[(size_t)e * p.cap_rows + (size_t)j * 128 + r]);
+                const int hm = (int)mraw.y >> 8;
+                const uint32_t g = mraw.x / G;
+                const uint32_t th = tokens_of_rank(p, hm);
+                const uint32_t cnt = min(G, th - g * G);
+                uint32_t got;
+                if (S && hm != p.rank)
+                  got = atom_add<true>(&p.peers[hm].grp_cnt[g], 1u) + 1u;
+                else
+                  got = atom_add<false>(&p.peers[hm].grp_cnt[g], 1u) + 1u;
+                if (got == cnt * (uint32_t)p.K) {
+#pragma unroll
+                  for (uint32_t c = 0; c < 4u; ++c) {
+                    if (c == nc) {
+                      c_home[c] = (uint32_t)hm;
+                      c_first[c] = g * G;
+                      c_ntok[c] = cnt;
+                    }
+                  }
+                  ++nc;
+                }
+              }
+            }
+            uint32_t ticket[4];
+            bool any_remote = false;
+#pragma unroll
+            for (uint32_t c = 0; c < 4u; ++c) {
+              ticket[c] = 0u;
+              if (c < nc) {
+                const FdmoePeer& hp = p.peers[c_home[c]];
+                const bool rem = S && (int)c_home[c] != p.rank;
+                any_remote |= rem;
+                ticket[c] = rem ? atom_add<true>(&hp.ctl->q[0].head, 1u) : atom_add<false>(&hp.ctl->q[0].head, 1u);
+                FdmoeSlot* sl = &hp.slots[0][ticket[c] & (uint32_t)p.queue_mask];
+                sl->a = FDMOE_TASK_COMBINE;
+                sl->b = c_first[c];
+                sl->c = c_ntok[c];
+              }
+            }
+            if (__any_sync(0xffffffffu, nc != 0u)) {
+              if (__any_sync(0xffffffffu, any_remote))
+                fence_acqrel<true>();
+              else
+                fence_acqrel<false>();
+#pragma unroll
+              for (uint32_t c = 0; c < 4u; ++c) {
+                if (c < nc) {
+                  const FdmoePeer& hp = p.peers[c_home[c]];
+                  if (S && (int)c_home[c] != p.rank) {
+                    st_relaxed<true>(&hp.slots[0][ticket[c] & (uint32_t)p.queue_mask].seq, ticket[c] + 1u);
+                    atom_add<true>(&hp.ctl->q[0].avail, 1u);
+                  } else {
+                    st_relaxed<false>(&hp.slots[0][ticket[c] & (uint32_t)p.queue_mask].seq, ticket[c] + 1u);
+                    atom_add<false>(&hp.ctl->q[0].avail, 1u);
+                  }
+                }
+              }
+            }
+            __syncwarp();
+            if (lane == 0) {
+              atomicAdd(&ctl->mtiles_done, 1u);
+              maybe_close(p);
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&sc.done_empty[d]);
+      }
     }
     __syncwarp();
   }
@@ -1794,12 +1843,14 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
     fence_acqrel<false>();
     const uint32_t prev = atomicAdd(&ctl->exit_cnt, 1u);
     if (prev == gridDim.x - 1u) {
-      // last CTA out: every pushed task was consumed, tickets taken by workers
-      // that left on `closed` are skipped, and the rank is reopened for the next
-      // launch (an aborted launch stays closed until the host re-creates it).
+      // last CTA out: whatever is left in the queues (nothing after a clean launch) is dropped and
+      // the rank is reopened for the next launch (an aborted launch stays closed until the host
+      // re-creates it).
       fence_acqrel<false>();
-      const uint32_t tail = ld_relaxed<false>(&ctl->q_tail);
-      st_relaxed<false>(&ctl->q_head, tail);
+      for (int qi = 0; qi < 3; ++qi) {
+        st_relaxed<false>(&ctl->q[qi].tail, ld_relaxed<false>(&ctl->q[qi].head));
+        st_relaxed<false>(&ctl->q[qi].avail, 0u);
+      }
       st_relaxed<false>(&ctl->exit_cnt, 0u);
       if (ld_relaxed<false>(&ctl->closed) == 1u) st_relaxed<false>(&ctl->closed, 0u);
     }

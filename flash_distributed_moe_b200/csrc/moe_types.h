@@ -17,44 +17,47 @@ enum {
   FDMOE_TILE_N2 = 256,   // FFN2: hidden columns per tile
   FDMOE_TILE_K = 64,     // one 128-byte swizzle atom of bf16 per stage
   FDMOE_GATE_TOKENS = 128,  // tokens per gate tile (one tcgen05 M tile)
-  FDMOE_PACK_ROWS = 72,     // rows per PACK task (rows of one expert, sent by one rank)
 };
 
-// Task kinds held by the global work queue.
+// Task kinds.  A rank has three queues: queue 0 (taken first) holds what unblocks other work or
+// frees memory early (FFN2 tiles, COMBINE groups, exact re-gating, the GATED round), queue 1 the
+// FFN1 tiles, queue 2 the DISPATCH tasks, of which only a few run at a time when rows cross
+// NVLink (the links, not the SMs, set their pace).  GATE tiles are not queued: workers claim them
+// from a counter.
 enum {
   FDMOE_TASK_NONE = 0,
   FDMOE_TASK_FFN1 = 1,     // (expert, m_tile, n_tile, rows): SwiGLU tile
   FDMOE_TASK_FFN2 = 2,     // (expert, m_tile, n_tile, rows): down-projection tile
-  FDMOE_TASK_COMBINE = 3,  // (token group): ordered sum over the K slots
-  FDMOE_TASK_GATED = 4,    // every rank has finished gating: row counts are final, start the dispatch
+  FDMOE_TASK_COMBINE = 3,  // (first token, count): ordered sum over the K slots
+  FDMOE_TASK_GATED = 4,    // every rank has finished gating: row counts are final, publish what is left
   FDMOE_TASK_TESTA = 5,    // task-system self test: x[i] *= 2 over a chunk, then push TESTB
   FDMOE_TASK_TESTB = 6,    // task-system self test: x[i] += 1 over a chunk
   FDMOE_TASK_EXIT = 7,
   FDMOE_TASK_GATE = 8,     // (token tile): gate GEMM, top-k, softmax, row reservation
-  FDMOE_TASK_PACK = 9,     // (expert, first entry, count): copy this rank's rows for one expert to its owner
-  FDMOE_TASK_GATEFIX = 10, // (token, token): exact fp32 gate of nearly tied tokens
+  FDMOE_TASK_DISPATCH = 9, // (first token, count): copies the tokens' rows into the owners' expert buffers
+  FDMOE_TASK_GATEFIX = 10, // (token, token): exact fp32 gate of nearly tied tokens and their dispatch
 };
 
 // Status codes written by the kernel (first error wins).
 enum {
   FDMOE_OK = 0,
-  FDMOE_ERR_TIMEOUT_QUEUE = 1,   // a worker waited too long for its ticket
+  FDMOE_ERR_TIMEOUT_QUEUE = 1,   // a worker found no work for too long, or a claimed slot was never published
   FDMOE_ERR_TIMEOUT_RING = 2,    // CTA-internal task ring
   FDMOE_ERR_TIMEOUT_STAGE = 3,   // TMA/MMA shared-memory stage barrier
   FDMOE_ERR_TIMEOUT_TMEM = 4,    // accumulator hand-off barrier
-  FDMOE_ERR_TIMEOUT_PEER = 5,    // a peer rank never signalled readiness
+  FDMOE_ERR_TIMEOUT_PEER = 5,    // a peer rank never entered the launch
   FDMOE_ERR_QUEUE_OVERFLOW = 6,
   FDMOE_ERR_BAD_TASK = 7,
   FDMOE_ERR_ROW_OVERFLOW = 8,    // more rows for an expert than its buffer holds
 };
 
-// One slot of the ticket queue (16 bytes).  `seq` == ticket + 1 once the slot
+// One slot of a task queue (16 bytes).  `seq` == ticket + 1 once the slot
 // holds the task of that ticket.
 typedef struct {
   uint32_t seq;
   uint32_t a;  // kind | expert << 8 | n_tile << 20
-  uint32_t b;  // m_tile, or token group, or chunk index
-  uint32_t c;  // valid rows in the tile
+  uint32_t b;  // m_tile, or first token, or chunk index
+  uint32_t c;  // valid rows in the tile, or token count
 } FdmoeSlot;
 
 // Sideband of one packed row (16 bytes): where its result goes.
@@ -65,48 +68,52 @@ typedef struct {
   int32_t pad;
 } FdmoeRowMeta;
 
+// State of one task queue, on a 128-byte line of its own.  Producers (this rank and its peers)
+// take tickets from `head` and add what they have published to `avail`; this rank's workers take
+// a unit of `avail` (a signed count) and then a ticket from `tail`.
+typedef struct {
+  uint32_t head;
+  uint32_t tail;
+  uint32_t avail;
+  uint32_t pad[29];
+} FdmoeQueueCtl;
+
 // Per-rank control block.  Lives in the rank's symmetric arena so that peers
 // can reach it.  Fields on separate 128-byte lines are written by different
 // agents.
 typedef struct {
-  // --- persistent queue state (never zeroed between launches)
-  uint32_t q_head;
-  uint32_t pad0[31];
-  uint32_t q_tail;
-  uint32_t pad1[31];
+  // --- persistent state (never zeroed between launches)
+  FdmoeQueueCtl q[3];
   uint32_t closed;  // 0 running, 1 finished, 2 aborted
   uint32_t status;  // first error code
   uint32_t status_info;
   uint32_t exit_cnt;
-  uint32_t urgent;  // a task that goes before the queue: 0, or 0x80000000 | kind | b << 8 (cleared by whoever takes it)
-  uint32_t pad2[27];
+  uint32_t pad2[28];
   uint32_t ready[32];  // ready[r] = launch epoch of peer r (written by peer r)
+  uint32_t tokens_of[2][16];  // [epoch & 1][r] = tokens of rank r in that launch (written by rank r)
   // --- per-launch counters: [launch_begin, launch_end) is zeroed before each launch
   uint32_t launch_begin;
-  uint32_t gated_tokens;     // tokens of this rank whose routing is decided
-  uint32_t rows_arrived;     // weighted rows of this rank's tokens that have come back (T*K when complete)
+  uint32_t gated_tokens;     // tokens of this rank whose routing is decided and whose rows have landed
   uint32_t ranks_gated;      // ranks whose gating is finished (incl. this one)
-  uint32_t gated_done;        // the GATED task of this launch has run (tile total and pack list are set)
+  uint32_t gated_done;       // the second gating round of this launch has run (tile total is set)
   uint32_t mtiles_total;     // m-tiles of this rank's experts this launch
   uint32_t mtiles_done;      // m-tiles whose FFN2 is complete
   uint32_t tokens_combined;
   uint32_t tokens_launch;    // tokens of this rank this launch (written at kernel start)
   uint32_t executed;         // tasks finished (used only with expected_static)
-  uint32_t pack_total;       // PACK tasks of this rank this launch (entries of its pack list)
-  uint32_t pack_cursor;      // next entry of the pack list to publish
-  uint32_t gate_tiles_done;  // GATE tiles of this rank that have finished
-  uint32_t round2_rdv;       // 2 when both this rank's first round is laid out and every rank has gated
-  uint32_t pad3[18];
+  uint32_t gate_next;        // next GATE tile to claim
+  uint32_t disp_active;      // DISPATCH tasks being worked on
+  uint32_t pad3[21];
 } FdmoeCtl;
 
 // What one rank can reach of a peer (or of itself): all device pointers valid
 // in this process.
 typedef struct {
   FdmoeCtl* ctl;
-  FdmoeSlot* slots;
-  uint32_t* expert_cnt;    // [El]       rows allocated per local expert
-  uint32_t* landed;        // [El]       rows landed per local expert
-  uint32_t* published;     // [El]       1 once the expert's FFN1 tiles have been published
+  FdmoeSlot* slots[3];     // the task queues
+  uint32_t* expert_cnt;    // [El]       rows reserved per local expert
+  uint32_t* landed;        // [El * MT]  rows landed per local expert and batch of m-tiles (batch b at [le * MT + b])
+  uint32_t* grp_cnt;       // [groups]   weighted rows that have come back, per COMBINE group of this rank's tokens
   void* packed;            // bf16 [El * cap_rows, H]
   FdmoeRowMeta* meta;      // [El * cap_rows]
   void* ystage;            // bf16 [max_tokens, K, H]
@@ -134,15 +141,16 @@ typedef struct {
   int32_t T;            // tokens this launch
   int32_t cap_rows;     // rows per expert buffer (multiple of 128)
   int32_t MT;           // cap_rows / 128
-  int32_t queue_mask;   // capacity - 1 (capacity is a power of two)
-  int32_t combine_group;  // most tokens per COMBINE task
+  int32_t queue_mask;   // capacity - 1 of either queue (capacity is a power of two)
+  int32_t combine_group;  // tokens per COMBINE task
   int32_t gate_rows;    // tokens per GATE task: 32, 64 or 128 (rows of the 128-row MMA tile that are used)
+  int32_t disp_conc;    // DISPATCH tasks worked on at a time
+  int32_t batch_mt;     // m-tiles per publication batch; 0 = chosen from the token counts of the launch
   int32_t mode;         // 0 full layer; 2 static tasks only (no gate)
-  int32_t debug_flags;  // timing experiments only (results become invalid): 1 skip FFN stores,
-                        // 2 skip completion fences, 4 skip proxy fences, 8 skip the operand loads of FFN tiles
   uint32_t expected_static;  // mode 2: tasks pre-filled by the host
   uint32_t epoch;       // launch counter (identical on all ranks)
-  uint64_t timeout_ns;  // budget of every device-side wait
+  uint64_t timeout_ns;       // budget of every device-side wait inside a launch
+  uint64_t peer_timeout_ns;  // budget of the wait for the peers to enter the launch
 
   const void* x;        // bf16 [T, H]
   void* out;            // bf16 [T, H] (may alias x)
@@ -150,16 +158,7 @@ typedef struct {
   void* act;            // bf16 [El * cap_rows, I]
   int32_t* topk_idx;    // [max_tokens, K]
   float* topk_w;        // [max_tokens, K]
-  // this rank's send lists, one per (global) expert: entry i of expert e is at [e * send_stride + i]
-  uint32_t* send_cnt;   // [E] entries per expert (zeroed per launch)
-  int32_t* send_src;    // token << 4 | slot
-  int32_t* send_dst;    // row in the owner's expert buffers
-  int32_t send_stride;  // = max tokens of this rank (an expert gets at most one row per token)
-  // this rank's PACK tasks of the launch in sending order, {a, b, c, 0} each; `pack_window` of them
-  // are outstanding at a time (every finished PACK task publishes the next entry)
-  uint32_t* pack_list;
-  int32_t pack_window;
-  int32_t pack_early;   // 1: packing starts when this rank's GATE tiles are done; 0: when every rank has gated
+  uint8_t* tok_flag;    // [max_tokens] 1: nearly tied token, routed and sent by its GATEFIX task
   uint32_t* ffn1_done;  // [El * MT]
   uint32_t* ffn2_done;  // [El * MT]
   uint32_t* status_host;  // mapped pinned word: first error code, readable without a sync

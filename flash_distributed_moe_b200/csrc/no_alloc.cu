@@ -15,8 +15,10 @@
 //     batches are rejected with cudaErrorInvalidValue and a message.  Every GPU
 //     on which this library is loaded holds those 32 MiB until the process ends;
 //   * the first call on a device resolves the array's device address and raises
-//     the kernel's shared-memory limit.  Make that first call outside of any
-//     stream capture;
+//     the kernel's shared-memory limit; with lazy module loading it may also be
+//     the moment the 32 MiB become resident on that device.  Make that first call
+//     early: before any stream capture and before the host freezes its memory
+//     budget;
 //   * every call uses the same array and begins by clearing the part of it that
 //     has to start from zero (queue, counters, status).  Two calls that overlap
 //     on the GPU (different streams, or threads) would corrupt each other: keep
@@ -109,12 +111,16 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
       (tokensNum > 0 && (!tokens || !output)))
     return (int)cudaErrorInvalidValue;
 
-  std::lock_guard<std::mutex> lock(g_mutex);  // host-side bookkeeping only; GPU-side overlap is the caller's duty
   int dev = 0;
   NA_CHECK(cudaGetDevice(&dev));
   PerDevice* d = nullptr;
-  const int rc = SetUpDevice(dev, &d);
-  if (rc != 0) return rc;
+  {
+    // the lock covers the one-time set-up only: every device has its own copy of the array, and
+    // keeping calls on one device apart is the caller's duty
+    std::lock_guard<std::mutex> lock(g_mutex);
+    const int rc = SetUpDevice(dev, &d);
+    if (rc != 0) return rc;
+  }
 
   // ---- geometry of this call (same rules as the launcher's Init, world size 1)
   Geometry g;
@@ -128,7 +134,7 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   g.max_tokens_sum = g.max_tokens_max;
   g.cap_rows = (int)AlignUp((size_t)g.max_tokens_sum, FDMOE_TILE_M);
   g.MT = g.cap_rows / FDMOE_TILE_M;
-  g.combine_group = 16;
+  g.combine_group = 8;
   g.queue_cap = QueueCapacity(g, d->grid);
   const ArenaLayout L = MakeLayout(g);
   // regions the launcher allocates separately follow the arena inside the same array
@@ -139,12 +145,8 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   off += AlignUp((size_t)g.max_tokens_max * g.K * 4, 256);
   const size_t off_w = off;
   off += AlignUp((size_t)g.max_tokens_max * g.K * 4, 256);
-  const size_t off_src = off;
-  off += AlignUp((size_t)g.E * AlignUp((size_t)g.max_tokens_max, 4) * 4 + 16, 256);
   const size_t off_dst = off;
-  off += AlignUp((size_t)g.E * AlignUp((size_t)g.max_tokens_max, 4) * 4 + 16, 256);
-  const size_t off_plist = off;
-  off += AlignUp(PackListBytes(g, g.max_tokens_max), 256);
+  off += AlignUp((size_t)g.max_tokens_max, 256);
   if (off > kScratchBytes) {
     MOE_ERROR_LOG("FlashMoeLaunchNoAlloc: this call needs %zu bytes of scratch, the fixed array holds %zu "
                   "(H=%d I=%d E=%d K=%d tokens=%d); use CreateLauncher/Launch for larger problems",
@@ -171,10 +173,12 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
     NA_CHECK(MakeTensorMap(d->encode, &p.tm_x, tokens, (uint64_t)tokensNum, g.H, std::min(p.gate_rows, tokensNum)));
   FdmoePeer& me = p.peers[0];
   me.ctl = reinterpret_cast<FdmoeCtl*>(base + L.ctl);
-  me.slots = reinterpret_cast<FdmoeSlot*>(base + L.slots);
+  me.slots[0] = reinterpret_cast<FdmoeSlot*>(base + L.slots[0]);
+  me.slots[1] = reinterpret_cast<FdmoeSlot*>(base + L.slots[1]);
+  me.slots[2] = reinterpret_cast<FdmoeSlot*>(base + L.slots[2]);
   me.expert_cnt = reinterpret_cast<uint32_t*>(base + L.expert_cnt);
   me.landed = reinterpret_cast<uint32_t*>(base + L.landed);
-  me.published = reinterpret_cast<uint32_t*>(base + L.published);
+  me.grp_cnt = reinterpret_cast<uint32_t*>(base + L.grp_cnt);
   me.packed = base + L.packed;
   me.meta = reinterpret_cast<FdmoeRowMeta*>(base + L.meta);
   me.ystage = base + L.ystage;
@@ -192,20 +196,17 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   p.combine_group = g.combine_group;
   p.mode = 0;
   p.epoch = 1;
+  p.disp_conc = d->grid;
+  p.batch_mt = 0;
   p.timeout_ns = 2000ull * 1000000ull;
+  p.peer_timeout_ns = p.timeout_ns;
   p.x = tokens;
   p.out = output;
   p.gate_w = gateWeights;
   p.act = base + off_act;
   p.topk_idx = reinterpret_cast<int32_t*>(base + off_idx);
   p.topk_w = reinterpret_cast<float*>(base + off_w);
-  p.send_cnt = reinterpret_cast<uint32_t*>(base + L.send_cnt);
-  p.send_src = reinterpret_cast<int32_t*>(base + off_src);
-  p.send_dst = reinterpret_cast<int32_t*>(base + off_dst);
-  p.pack_list = reinterpret_cast<uint32_t*>(base + off_plist);
-  p.pack_window = 1 << 30;
-  p.pack_early = 1;
-  p.send_stride = (int32_t)AlignUp((size_t)g.max_tokens_max, 4);
+  p.tok_flag = base + off_dst;
   p.ffn1_done = reinterpret_cast<uint32_t*>(base + L.ffn1_done);
   p.ffn2_done = reinterpret_cast<uint32_t*>(base + L.ffn2_done);
   NA_CHECK(fdmoe_kernel_launch(&p, d->grid, stream));

@@ -85,25 +85,19 @@ int FlashMoeTestTaskSystem(FlashMoeHandle h, int32_t* data, int n, void* stream)
 int FlashMoeTestQueueGemm(FlashMoeHandle h, const uint32_t* rowsPerExpertHost, const void* A,
                           void* out, void* stream);
 
-/* Self-test of the CTA-pair tensor-core primitive under the FFN tiles (no counterpart in the
- * reference): one cluster of two CTAs computes D[256, N] = W[256, K] * X[N, K]^T with
- * tcgen05.mma.cta_group::2, X arriving in boxes of `boxRows` rows.  W, X bf16 and D fp32 are
- * device pointers; N a multiple of 16 in [16, 256], K a multiple of 64, boxRows a multiple of 8
- * dividing N/2.  `mainLoopNs` (may be NULL) receives the duration of the MMA issue loop in ns.
- * Synchronous. */
-int FlashMoeTestPairGemm(const void* W, const void* X, float* D, int N, int K, int boxRows,
-                         unsigned* mainLoopNs, void* stream);
-
 /* The whole layer in one call that allocates nothing (no counterpart in the reference, whose
  * launcher always allocates its scratch in Init, src/hip/launcher/moeKernelLauncher.hip:139-165).
  * For callers that may not touch the device allocator: an engine that has frozen its memory pool,
  * a callback that must not call allocating runtime functions, a process whose memory belongs to
  * another allocator.  All scratch comes from a fixed 32 MiB array inside the library image (held
  * on every GPU that loads the library); a call whose scratch does not fit is rejected with
- * cudaErrorInvalidValue.  Single rank, bf16, device pointers; config == NULL selects the
- * Qwen3-30B-A3B shape.  The first call on a device does one-time set-up and should be made
- * outside of stream capture.  Calls share the array: do not let two of them overlap on a GPU.
- * Returns after the layer has finished; a device-side error is reported as cudaErrorUnknown. */
+ * cudaErrorInvalidValue.  Single rank, bf16, device pointers.  config == NULL means the
+ * Qwen3-30B-A3B shape, whose 128 expert buffers alone exceed the array, so that call is always
+ * rejected: pass the (smaller) layer you run.  The first call on a device does one-time set-up (it
+ * may be the moment the 32 MiB become resident there): make it before any stream capture and before
+ * the host freezes its memory budget.  Calls share the array: do not let two of them overlap on a
+ * GPU.  Every call synchronises `stream` and returns after the layer has finished; a device-side
+ * error is reported as cudaErrorUnknown. */
 int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1ExpertWeights,
                           const void* ffn2ExpertWeights, const void* tokens, void* output, int tokensNum,
                           const FlashMoeConfig* config, void* stream);

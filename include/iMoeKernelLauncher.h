@@ -19,8 +19,10 @@
 //
 // The reference fixes shape and dtype at compile time (Qwen3-30B-A3B, fp32).
 // This build takes them at run time through CreateLauncherEx; CreateLauncher
-// keeps the reference's implicit shape (hidden 2048, 128 experts, top-8,
-// intermediate 768) with bf16 tensors.
+// keeps the reference's implicit layer exactly: hidden 2048, 128 experts, top-8,
+// intermediate 768, and fp32 weights, tokens and output (converted to bf16 at the
+// boundary), so a caller written against the reference header gets what it
+// expects.  bf16 tensors, the native path, go through CreateLauncherEx.
 #pragma once
 
 #include <cuda_runtime_api.h>
@@ -70,7 +72,7 @@ struct MoeConfig {
 // (reference: include/iMoeKernelLauncher.h:26, src/moeKernelLauncher.cpp:15-30).
 extern "C" moe::DistributedUniqueId GetDistributedUniqueId(bool empty);
 
-// Creates a launcher for the Qwen3-30B-A3B layer shape, bf16
+// Creates a launcher for the reference's layer: Qwen3-30B-A3B shape, fp32 tensors
 // (reference: include/iMoeKernelLauncher.h:29-35, src/moeKernelLauncher.cpp:33-46).
 // *launcher is written only on success.
 extern "C" cudaError_t CreateLauncher(moe::IMoeKernelLauncher** launcher,
@@ -81,8 +83,9 @@ extern "C" cudaError_t CreateLauncher(moe::IMoeKernelLauncher** launcher,
                                       const moe::DistributedUniqueId& uid,
                                       int rank, int worldSize);
 
-// Same, with the layer shape and dtype given at run time.  The reference has no
-// such call: its shape is the compile-time struct src/hip/common/metadata.h:7-13.
+// Same, with the layer shape and dtype given at run time (config == NULL: the
+// Qwen3-30B-A3B shape with bf16 tensors).  The reference has no such call: its
+// shape is the compile-time struct src/hip/common/metadata.h:7-13.
 extern "C" cudaError_t CreateLauncherEx(moe::IMoeKernelLauncher** launcher,
                                         const void* gateWeights,
                                         const void* ffn1ExpertWeights,

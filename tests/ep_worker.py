@@ -20,8 +20,8 @@ from moe_testlib import cpu_oracle, synth  # noqa: E402
 
 def main():
     # Ranks check their slices against the CPU oracle between launches and so reach the next (collective)
-    # launch seconds apart, a rank without tokens at once: give the device-side wait for the peers room.
-    os.environ.setdefault("FLASHMOE_TIMEOUT_MS", "120000")
+    # launch seconds apart, a rank without tokens at once: the library's own budget for peers to enter a
+    # launch (FLASHMOE_PEER_TIMEOUT_MS, 60 s by default) covers that; the waits inside a launch keep theirs.
     rank, world = int(sys.argv[1]), int(sys.argv[2])
     uid = bytes.fromhex(sys.argv[3])
     case = sys.argv[4]
