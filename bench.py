@@ -2,13 +2,17 @@
 """MoE-layer throughput benchmark (tokens/s) for the B200 FlashDMoE launcher.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+                    [--shape 30b|235b] [--tokens T] [--skew none|zipf]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 A step is one `Launch` of the layer over one batch of synthetic tokens (seeded N(0,1) bf16
 activations, N(0,0.02) bf16 weights; real Qwen3 checkpoints are not available offline).  Default
 workload: the Qwen3-30B-A3B layer shape (hidden 2048, 128 experts, top-8, intermediate 768) at 4096
 tokens per GPU; with N > 1 the experts are sharded over the ranks (expert parallelism) and the
-tokens per GPU stay fixed (weak scaling).  Rank 0 prints ONE JSON line.
+tokens per GPU stay fixed (weak scaling).  `--skew zipf` biases the gate so that expert popularity
+follows Zipf(1.2).  Before anything is timed, every rank checks a sample of its tokens against the
+CPU oracle (top-k indices exact, output within max-abs 2e-2 / rel-L2 1e-2).  Rank 0 prints ONE JSON
+line.
 
 `--impl reference` times the reference project's own CPU MoE (oracle/_ref when it was built from
 the reference sources, else the C restatement under oracle/) on the host cores, on a bounded sample
@@ -33,6 +37,7 @@ from flash_distributed_moe_b200 import synth  # noqa: E402
 
 SHAPES = {"30b": synth.QWEN3_30B_A3B, "235b": synth.QWEN3_235B_A22B}
 L2_BYTES = 126e6
+MAX_ABS, REL_L2 = 2e-2, 1e-2
 
 
 def flops_per_token(s) -> float:
@@ -49,8 +54,8 @@ def algorithmic_bytes(s, tokens, world) -> float:
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the persistent kernel from ncu, for the
-# workloads that were captured (profiles/moe_persistent_kernel_dram_traffic_qwen3-30b_4096tok.md)
-MEASURED_TRAFFIC = {("30b", 4096, 1): 1.591e9 + 332.1e6}
+# workloads that were captured (profiles/): (shape, tokens per GPU, GPUs) -> bytes
+MEASURED_TRAFFIC = {}
 
 
 def measured_peaks():
@@ -121,31 +126,101 @@ def dist_env():
     return rank, world, local
 
 
-def make_gpu_inputs(shape, tokens, rank, world, device):
-    """Weights and tokens generated on the device from fixed seeds (bf16)."""
-    el = shape.experts // world
+def workload_name(shape, tokens, world, skew) -> str:
+    routing = "random gate" if skew == "none" else "gate biased to Zipf(1.2) expert popularity"
+    return (f"{shape.name} MoE layer, {tokens} tokens per GPU, top-{shape.topk} of {shape.experts} experts, "
+            f"{routing}, experts sharded over {world} GPU(s)")
+
+
+def make_gate_and_tokens(shape, tokens, rank, device, skew):
+    """Gate weights (identical on all ranks) and this rank's tokens, bf16 on the device.  With
+    skew == "zipf" the last activation column is 1 and the gate column holds a per-expert bias
+    (reference construction: test/common/moeTools.h:187-207); returns the realised popularity too."""
     g = torch.Generator(device=device).manual_seed(0)
     gate = (torch.randn(shape.experts, shape.hidden, generator=g, device=device) * 0.02).to(torch.bfloat16)
+    gt = torch.Generator(device=device).manual_seed(7 + rank)
+    x = torch.randn(tokens, shape.hidden, generator=gt, device=device).to(torch.bfloat16)
+    info = None
+    if skew == "zipf":
+        gate_c, x_c, info = synth.zipf_routing(shape, gate.cpu(), x.cpu(), s=1.2, seed=0)
+        gate, x = gate_c.to(device), x_c.to(device)
+    return gate, x, info
+
+
+def make_expert_shard(shape, rank, world, device):
+    """This rank's contiguous shard of the expert weights, generated on the device (one seed per rank;
+    the parity check reads back what the GPUs really hold, so the set need not be independent of the
+    sharding)."""
+    el = shape.experts // world
     ge = torch.Generator(device=device).manual_seed(1000 + rank)
     w13 = (torch.randn(el, 2 * shape.inter, shape.hidden, generator=ge, device=device) * 0.02).to(torch.bfloat16)
     w2 = (torch.randn(el, shape.hidden, shape.inter, generator=ge, device=device) * 0.02).to(torch.bfloat16)
-    gt = torch.Generator(device=device).manual_seed(7 + rank)
-    x = torch.randn(tokens, shape.hidden, generator=gt, device=device).to(torch.bfloat16)
-    return gate, w13, w2, x
+    return w13, w2
+
+
+class SharedWeights:
+    """All ranks' expert shards as bf16 bit patterns in one memory-mapped file that every rank can read
+    (each rank writes the shard its GPU really uses), for the CPU oracle's parity check."""
+
+    def __init__(self, shape, rank, world, w13, w2, barrier):
+        base = "/dev/shm" if os.path.isdir("/dev/shm") and os.access("/dev/shm", os.W_OK) else "/tmp"
+        tag = os.environ.get("MASTER_PORT", "0") + "_" + str(os.getppid() if world > 1 else os.getpid())
+        self.paths = [os.path.join(base, f"flashmoe_bench_{tag}_{n}.bin") for n in ("w13", "w2")]
+        E, H, I = shape.experts, shape.hidden, shape.inter
+        el = E // world
+        shapes = [(E, 2 * I, H), (E, H, I)]
+        self.rank = rank
+        if rank == 0:
+            for p, shp in zip(self.paths, shapes):
+                np.lib.format.open_memmap(p, mode="w+", dtype=np.uint16, shape=shp).flush()
+        barrier()
+        self.maps = [np.load(p, mmap_mode="r+") for p in self.paths]
+        for m, t in zip(self.maps, (w13, w2)):
+            m[rank * el:(rank + 1) * el] = t.cpu().view(torch.int16).numpy().view(np.uint16)
+            m.flush()
+        barrier()
+
+    def close(self, barrier):
+        self.maps = None
+        barrier()
+        if self.rank == 0:
+            for p in self.paths:
+                try:
+                    os.remove(p)
+                except OSError:
+                    pass
+
+
+def parity_check(shape, launcher, shared, gate, x, out, n_check, threads):
+    """Top-k indices (exact) and output (north-star tolerances) of a sample of this rank's tokens
+    against the CPU oracle.  This and cpu_baseline_leg are the only places the b200 arm touches oracle/."""
+    from oracle import cpu_oracle
+    port = cpu_oracle.PortOracle()
+    T = x.shape[0]
+    n = min(n_check, T)
+    if n == 0:
+        return {"tokens_checked": 0, "topk_mismatch_tokens": 0, "max_abs": 0.0, "rel_l2": 0.0, "pass": True}
+    sel = np.unique(np.linspace(0, T - 1, n).astype(np.int64))
+    xs = np.ascontiguousarray(x[torch.from_numpy(sel).to(x.device)].float().cpu().numpy())
+    ref, _, ref_idx = port.full_moe_bf16_weights(xs, np.ascontiguousarray(gate.float().cpu().numpy()),
+                                                 shared.maps[0], shared.maps[1], shape.topk, threads=threads)
+    idx = np.frombuffer(launcher.debug_read(0, T * shape.topk * 4), np.int32).reshape(T, shape.topk)[sel]
+    got = out[torch.from_numpy(sel).to(out.device)].float().cpu().numpy()
+    mism = int((idx != ref_idx).any(axis=1).sum())
+    max_abs = float(np.abs(got - ref).max())
+    rel = float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30))
+    return {"tokens_checked": int(len(sel)), "topk_mismatch_tokens": mism, "max_abs": max_abs, "rel_l2": rel,
+            "pass": bool(mism == 0 and max_abs <= MAX_ABS and rel <= REL_L2)}
 
 
 def cpu_reference_run(oracle, xf, gf, w13f, w2f, topk, threads):
     t0 = time.perf_counter()
-    if oracle.kind == "reference":
-        out = oracle.full_moe(xf, gf, w13f, w2f, topk, threads=threads)
-    else:
-        out = oracle.full_moe(xf, gf, w13f, w2f, topk, threads=threads)
+    out = oracle.full_moe(xf, gf, w13f, w2f, topk, threads=threads)
     return out, time.perf_counter() - t0
 
 
-def cpu_baseline_leg(shape, gate, w13, w2, x, gpu_out, budget_s=15.0):
-    """Times the CPU reference on a bounded sample of the step's tokens (all host threads) and uses its
-    results to check the GPU output of those tokens.  This is the only place the b200 arm touches oracle/."""
+def cpu_baseline_leg(shape, gate, w13, w2, x, budget_s=12.0):
+    """Times the CPU reference on a bounded sample of the step's tokens with all host threads."""
     from oracle import cpu_oracle
     cpu_oracle.build()
     oracle = cpu_oracle.best_oracle()
@@ -153,21 +228,14 @@ def cpu_baseline_leg(shape, gate, w13, w2, x, gpu_out, budget_s=15.0):
     gf = gate.float().cpu().numpy()
     w13f = w13.float().cpu().numpy()
     w2f = w2.float().cpu().numpy()
-    xs = x.float().cpu().numpy()
+    xs = x[:max(4 * threads, 256)].float().cpu().numpy()
     probe = min(threads, xs.shape[0])
     _, dt = cpu_reference_run(oracle, xs[:probe], gf, w13f, w2f, shape.topk, threads)
     per_round = max(dt, 1e-3)
-    n = int(min(xs.shape[0], max(probe, probe * (budget_s / per_round))))
-    ref, dt = cpu_reference_run(oracle, xs[:n], gf, w13f, w2f, shape.topk, threads)
-    got = gpu_out[:n].float().cpu().numpy()
-    err = np.abs(got - ref)
-    parity = {"tokens_checked": n, "max_abs": float(err.max()),
-              "rel_l2": float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30)),
-              "tolerance": {"max_abs": 2e-2, "rel_l2": 1e-2}}
-    parity["pass"] = bool(parity["max_abs"] <= 2e-2 and parity["rel_l2"] <= 1e-2)
-    base = {"value": n / dt, "unit": "tokens/s", "cores": threads, "kind": oracle.kind,
+    n = int(min(xs.shape[0], max(probe, probe * int(budget_s / per_round))))
+    _, dt = cpu_reference_run(oracle, xs[:n], gf, w13f, w2f, shape.topk, threads)
+    return {"value": n / dt, "unit": "tokens/s", "cores": threads, "kind": oracle.kind,
             "sample": f"first {n} tokens of the step's batch, fp32, all host threads, {dt:.1f} s"}
-    return base, parity
 
 
 def run_reference_arm(args, shape):
@@ -180,6 +248,8 @@ def run_reference_arm(args, shape):
     threads = oracle.max_threads()
     gate, w13, w2 = synth.make_weights(shape, seed=0)
     x = synth.make_tokens(shape, max(threads * 4, 64), seed=0)
+    if args.skew == "zipf":
+        gate, x, _ = synth.zipf_routing(shape, gate, x, s=1.2, seed=0)
     gf, w13f, w2f, xf = [t.float().numpy() for t in (gate, w13, w2, x)]
     # bounded sample per step: calibrate one round of `threads` tokens, then size the step so that the
     # whole run stays within about two minutes
@@ -199,8 +269,8 @@ def run_reference_arm(args, shape):
         "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{shape.name} MoE layer, {args.tokens} tokens per GPU (CPU: sampled)",
-                   "hidden": shape.hidden, "experts": shape.experts, "topk": shape.topk, "inter": shape.inter},
+        "config": {"workload": workload_name(shape, args.tokens, args.gpus, args.skew),
+                   "hidden": shape.hidden, "inter": shape.inter, "tokens_per_gpu": args.tokens},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": oracle.kind, "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -216,6 +286,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--shape", default="30b", choices=sorted(SHAPES))
     ap.add_argument("--tokens", type=int, default=4096, help="tokens per GPU per step")
+    ap.add_argument("--skew", default="none", choices=["none", "zipf"], help="expert popularity")
+    ap.add_argument("--parity-tokens", type=int, default=512, help="tokens per rank checked against the CPU oracle")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     shape = SHAPES[args.shape]
@@ -240,8 +312,15 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
 
+    def barrier():
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(device)
+
     T = args.tokens
-    gate, w13, w2, x = make_gpu_inputs(shape, T, rank, world, device)
+    gate, x, skew_info = make_gate_and_tokens(shape, T, rank, device, args.skew)
+    w13, w2 = make_expert_shard(shape, rank, world, device)
     launcher = MoeKernelLauncher()
     if world > 1:
         box = [MoeKernelLauncher.getDistributedUniqueId() if rank == 0 else None]
@@ -252,11 +331,30 @@ def main():
     launcher.create(gate, w13, w2, T, uid, rank, world, topk=shape.topk)
     out = torch.empty_like(x)
 
-    def barrier():
-        torch.cuda.synchronize(device)
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize(device)
+    # ---- parity gate, before anything is timed: a sample of every rank's tokens against the CPU oracle
+    from oracle import cpu_oracle
+    if rank == 0:
+        cpu_oracle.build()
+    barrier()
+    shared = SharedWeights(shape, rank, world, w13, w2, barrier)
+    launcher.launch(x, out)
+    barrier()
+    code, info = launcher.last_status()
+    if code != 0:
+        raise SystemExit(f"device-side error {code} (info 0x{info:x}) in the parity launch")
+    threads = max(1, (os.cpu_count() or 1) // world)
+    par = parity_check(shape, launcher, shared, gate, x, out, args.parity_tokens, threads)
+    if world > 1:
+        t = torch.tensor([float(par["topk_mismatch_tokens"]), par["max_abs"], par["rel_l2"],
+                          0.0 if par["pass"] else 1.0], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        worst = [float(v) for v in t.tolist()]
+    else:
+        worst = [float(par["topk_mismatch_tokens"]), par["max_abs"], par["rel_l2"], 0.0 if par["pass"] else 1.0]
+    parity = {"tokens_checked_per_rank": par["tokens_checked"], "ranks": world,
+              "topk_mismatch_tokens_worst_rank": int(worst[0]), "max_abs": worst[1], "rel_l2": worst[2],
+              "tolerance": {"topk": "exact", "max_abs": MAX_ABS, "rel_l2": REL_L2}, "pass": worst[3] == 0.0}
+    shared.close(barrier)
 
     for _ in range(args.warmup):
         launcher.launch(x, out)
@@ -266,7 +364,7 @@ def main():
         raise SystemExit(f"device-side error {code} (info 0x{info:x}) during warm-up")
 
     # ---- device-resident timing: K launches, one event pair per launch (inputs stay in HBM; the
-    # 1.2 GB of expert weights read each step is larger than L2, so no flush is needed)
+    # expert weights read each step plus the row buffers written and read exceed L2, so no flush is needed)
     sampler = ClockSampler(local) if rank == 0 else None
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -304,9 +402,11 @@ def main():
     e2e_ok = torch.equal(h_out, out.cpu())
 
     if world > 1:
-        t = torch.tensor([total_ms, e2e_ms, max(per_launch_ms), statistics.mean(per_launch_ms)], device=device)
+        t = torch.tensor([total_ms, e2e_ms, max(per_launch_ms), statistics.mean(per_launch_ms),
+                          0.0 if e2e_ok else 1.0], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms, _, mean_launch_ms = [float(v) for v in t.tolist()]
+        total_ms, e2e_ms, _, mean_launch_ms, e2e_bad = [float(v) for v in t.tolist()]
+        e2e_ok = e2e_bad == 0.0
     else:
         mean_launch_ms = statistics.mean(per_launch_ms)
 
@@ -316,21 +416,26 @@ def main():
         tokens_total = T * world
         ms_per_step = total_ms / args.steps
         value = tokens_total / (ms_per_step * 1e-3)
-        flop_launch = flops_per_token(shape) * T  # per GPU under uniform routing
+        flop_launch = flops_per_token(shape) * T  # per GPU (every rank computes T*K pairs on average)
         achieved_tflops = flop_launch / (mean_launch_ms * 1e-3) / 1e12
+        expert_tflops = shape.topk * 6.0 * shape.hidden * shape.inter * T / (mean_launch_ms * 1e-3) / 1e12
         alg_bytes = algorithmic_bytes(shape, T, world)
         hbm_gbs = alg_bytes / (mean_launch_ms * 1e-3) / 1e9
+        config = {"workload": workload_name(shape, T, world, args.skew),
+                  "hidden": shape.hidden, "inter": shape.inter, "tokens_per_gpu": T,
+                  "l2_policy": "inputs larger than L2 (expert weights and row buffers touched per step exceed 126 MB)"}
+        if skew_info is not None:
+            config["routing_skew"] = skew_info
         result = {
             "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{shape.name} MoE layer, {T} tokens per GPU, top-{shape.topk} of {shape.experts} "
-                                   f"experts, random gate, experts sharded over {world} GPU(s)",
-                       "hidden": shape.hidden, "inter": shape.inter, "tokens_per_gpu": T,
-                       "l2_policy": "inputs larger than L2 (expert weights read per step exceed 126 MB)"},
+            "config": config,
             "roofline": {"bound": "tensor", "achieved": achieved_tflops, "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": achieved_tflops / peaks["bf16_tflops"],
-                         "traffic": MEASURED_TRAFFIC.get((args.shape, T, world)), "traffic_unit": "bytes/launch (ncu dram read+write)",
+                         "expert_gemm_tflops": expert_tflops, "expert_gemm_frac": expert_tflops / peaks["bf16_tflops"],
+                         "traffic": MEASURED_TRAFFIC.get((args.shape, T, world)),
+                         "traffic_unit": "bytes/launch (ncu dram read+write)",
                          "algorithmic_bytes": alg_bytes,
                          "peak_source": peaks["source"] + " burst",
                          "kernel": "moe_persistent_kernel", "kernel_ms": mean_launch_ms,
@@ -340,11 +445,10 @@ def main():
                     "matches_device_path": bool(e2e_ok)},
             "gpu_launches": args.steps,
             "clocks": clocks,
+            "parity": parity,
         }
         if world == 1 and not args.no_cpu_baseline:
-            base, parity = cpu_baseline_leg(shape, gate, w13, w2, x, out)
-            result["cpu_baseline"] = base
-            result["parity"] = parity
+            result["cpu_baseline"] = cpu_baseline_leg(shape, gate, w13, w2, x)
     launcher.destroy()
     if world > 1:
         dist.barrier()

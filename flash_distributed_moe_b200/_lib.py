@@ -16,7 +16,7 @@ EXPORTED_SYMBOLS = [
     "GetDistributedUniqueId", "CreateLauncher", "CreateLauncherEx", "DestroyLauncher",
     "FlashMoeGetUniqueId", "FlashMoeCreate", "FlashMoeLaunch", "FlashMoeLaunchHost",
     "FlashMoeDestroy", "FlashMoeGetLastStatus", "FlashMoeDebugRead", "FlashMoeTestTaskSystem",
-    "FlashMoeTestQueueGemm", "FlashMoeErrorString", "FlashMoeLaunchNoAlloc",
+    "FlashMoeTestQueueGemm", "FlashMoeTestStall", "FlashMoeErrorString", "FlashMoeLaunchNoAlloc",
 ]
 
 
@@ -50,6 +50,8 @@ def lib() -> C.CDLL:
     L.FlashMoeDebugRead.argtypes = [vp, C.c_int, vp, C.c_size_t, C.c_size_t]
     L.FlashMoeTestTaskSystem.argtypes = [vp, vp, C.c_int, vp]
     L.FlashMoeTestQueueGemm.argtypes = [vp, C.POINTER(C.c_uint32), vp, vp, vp]
+    L.FlashMoeTestStall.argtypes = [vp, vp]
+    L.FlashMoeTestStall.restype = C.c_int
     L.FlashMoeLaunchNoAlloc.argtypes = [vp, vp, vp, vp, vp, C.c_int, C.POINTER(FlashMoeConfig), vp]
     L.FlashMoeLaunchNoAlloc.restype = C.c_int
     L.FlashMoeErrorString.argtypes = [C.c_int]

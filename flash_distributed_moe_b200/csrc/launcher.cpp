@@ -68,6 +68,7 @@ class MoeKernelLauncher final : public moe::IMoeKernelLauncher {
   cudaError_t DebugRead(int which, void* dst, size_t offset, size_t bytes);
   cudaError_t TestTaskSystem(int32_t* data, int n, cudaStream_t stream);
   cudaError_t TestQueueGemm(const uint32_t* rowsPerExpert, const void* A, void* out, cudaStream_t stream);
+  cudaError_t TestStall(cudaStream_t stream);
   void LastStatus(uint32_t* code, uint32_t* info) const {
     if (code) *code = status_host_ ? status_host_[0] : 0;
     if (info) *info = status_host_ ? status_host_[1] : 0;
@@ -579,6 +580,13 @@ cudaError_t MoeKernelLauncher::TestTaskSystem(int32_t* data, int n, cudaStream_t
   return e;
 }
 
+// A launch that expects one task nobody ever publishes: every worker's bounded wait for work runs out,
+// the kernel records FDMOE_ERR_TIMEOUT_QUEUE and returns.
+cudaError_t MoeKernelLauncher::TestStall(cudaStream_t stream) {
+  if (!inited_) return cudaErrorNotReady;
+  return LaunchBf16(nullptr, nullptr, 0, stream, 2, 1u);
+}
+
 cudaError_t MoeKernelLauncher::TestQueueGemm(const uint32_t* rowsPerExpert, const void* A, void* out,
                                              cudaStream_t stream) {
   if (!inited_ || dtype_ != moe::MOE_DTYPE_BF16) return cudaErrorNotReady;
@@ -738,6 +746,11 @@ extern "C" int FlashMoeTestQueueGemm(FlashMoeHandle h, const uint32_t* rowsPerEx
                                      void* out, void* stream) {
   if (!h || !rowsPerExpertHost) return (int)cudaErrorInvalidValue;
   return (int)AsLauncher(h)->TestQueueGemm(rowsPerExpertHost, A, out, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int FlashMoeTestStall(FlashMoeHandle h, void* stream) {
+  if (!h) return (int)cudaErrorInvalidValue;
+  return (int)AsLauncher(h)->TestStall(static_cast<cudaStream_t>(stream));
 }
 
 extern "C" const char* FlashMoeErrorString(int code) { return cudaGetErrorString(static_cast<cudaError_t>(code)); }

@@ -80,11 +80,6 @@ struct __align__(64) SmemCtl {
   uint32_t run_round2;  // set by a task body that found this rank's GATED round due: the group runs it next
   uint32_t batch_mt;    // m-tiles per publication batch of this launch (identical on all ranks)
   uint32_t tokens_all;  // tokens of all ranks this launch
-  // Copy of the kernel parameters for the task bodies that are compiled as separate functions:
-  // there the parameter block is only reachable through a generic pointer, and every access to
-  // the constant bank through one costs on the order of a hundred cycles; shared memory does not.
-  // (TMA descriptors are always taken from the original.)
-  FdmoeParams params;
   // The epilogue group runs one task at a time, so the scratch of a GATE task
   // and the store staging of an FFN task share storage.  16-byte aligned: the
   // staging buffer is accessed with 16-byte vector loads and stores.
@@ -107,18 +102,31 @@ struct __align__(64) SmemCtl {
       float exact[2][128];
       uint2 fix_dst[2][FDMOE_MAX_TOPK];         // {expert, row in the owner's buffers} of each slot, or {~0, 0}
     };
-    // FFN epilogues: per-warp staging of a 32-row x 64-byte chunk (80-byte pitch
-    // keeps the 16-byte accesses of a quarter warp on distinct banks)
-    uint8_t store_stage[kEpiThreads / 32][32 * 80];
+    // FFN epilogues: per-warp staging of 32 rows x 128 bytes (chunks swizzled within a row)
+    uint8_t store_stage[kEpiThreads / 32][32 * 128];
   };
+  // Copy of the kernel parameters for the task bodies that are compiled as separate functions:
+  // there the parameter block is only reachable through a generic pointer, and every access to
+  // the constant bank through one costs on the order of a hundred cycles; shared memory does not.
+  // TMA descriptors are always taken from the original, so the copy leaves them out: it starts at
+  // the member after them (see task_params()).
+  alignas(64) uint8_t params_tail[sizeof(FdmoeParams) - offsetof(FdmoeParams, peers)];
 };
+
+// The parameter block as the out-of-line task bodies see it: every member from `peers` on is read
+// from the shared-memory copy; the TMA descriptors in front of it are not part of the copy and must
+// not be touched through this reference.
+__device__ __forceinline__ const FdmoeParams& task_params(const SmemCtl& sc) {
+  static_assert(offsetof(SmemCtl, params_tail) >= offsetof(FdmoeParams, peers), "the view must start inside SmemCtl");
+  return *reinterpret_cast<const FdmoeParams*>(reinterpret_cast<const uint8_t*>(&sc) +
+                                               (offsetof(SmemCtl, params_tail) - offsetof(FdmoeParams, peers)));
+}
 
 constexpr int kSmemBytes = kStages * kStageBytes + (int)sizeof(SmemCtl) + 1024;
 static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA exceeds the sm_100 limit");
 static_assert(offsetof(SmemCtl, xrow) % 16 == 0 && offsetof(SmemCtl, logit_tile) % 16 == 0 && (132 * 4) % 16 == 0,
               "vector accesses to the gate scratch need 16-byte alignment");
-static_assert(offsetof(SmemCtl, store_stage) % 16 == 0 && (32 * 80) % 16 == 0 && 80 % 16 == 0,
-              "store staging must keep 16-byte alignment for every warp and row");
+static_assert(offsetof(SmemCtl, store_stage) % 16 == 0, "store staging must keep 16-byte alignment");
 static_assert(offsetof(SmemCtl, full_bar) % 8 == 0 && offsetof(SmemCtl, ring) % 16 == 0, "barrier / ring alignment");
 
 // ------------------------------------------------------------ scoped helpers
@@ -268,9 +276,11 @@ __device__ __noinline__ void record_stuck(const FdmoeParams& p, SmemCtl& sc, uin
 }
 
 // Bounded mbarrier wait.  Returns false (after raising the error) on timeout
-// or when another role of this CTA has aborted.
+// or when another role of this CTA has aborted.  `budgets`: how many wait budgets to allow (the
+// roles that wait for the scheduler's next task allow two, so that a worker without work reports
+// the scheduler's own time-out).
 __device__ __forceinline__ bool wait_bar(const FdmoeParams& p, SmemCtl& sc, uint64_t* bar,
-                                         uint32_t parity, uint32_t err_code) {
+                                         uint32_t parity, uint32_t err_code, uint32_t budgets = 1u) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = ptx::globaltimer_ns();
   uint32_t spins = 0;
@@ -281,7 +291,7 @@ __device__ __forceinline__ bool wait_bar(const FdmoeParams& p, SmemCtl& sc, uint
         record_stuck(p, sc, bar, parity, err_code | 0x100u, waited);
         return false;
       }
-      if (waited > p.timeout_ns) {
+      if (waited > budgets * p.timeout_ns) {
         record_stuck(p, sc, bar, parity, err_code, waited);
         raise_error(p, sc, err_code, (blockIdx.x << 8) | (threadIdx.x >> 5));
         return false;
@@ -629,8 +639,8 @@ __device__ __forceinline__ void topk_warp(const float* logits, int E, int K, int
 // 128 tokens (TMEM lanes) x 128 experts (columns) as computed by the tensor
 // cores, whose accumulation order is not the reference's.  Measured on B200 the
 // two orders differ by at most 2.7e-9 * H of the logit scale.  A token whose
-// leading nine logits contain an adjacent pair closer than tau = 6e-8 * H of the
-// scale (more than ten times that difference on each side) is handed to a
+// leading nine logits contain an adjacent pair closer than tau = 3e-8 * H of the
+// scale (more than five times that difference on each side) is handed to a
 // GATEFIX task, which recomputes its logits in the reference's order; for every
 // other token both orders select the same experts in the same order.
 //
@@ -701,7 +711,7 @@ __device__ __noinline__ void gate_epilogue(const FdmoeParams& p, SmemCtl& sc, ui
   if (etid < FDMOE_GATE_TOKENS) {
     bool tie = false;
     if (etid < nt) {
-      const float tau = 6e-8f * (float)p.H * fmaxf(1.0f, fabsf(sc.top_v[etid][0]));
+      const float tau = 3e-8f * (float)p.H * fmaxf(1.0f, fabsf(sc.top_v[etid][0]));
       for (int j = 0; j + 1 < kk; ++j) tie |= (sc.top_v[etid][j] - sc.top_v[etid][j + 1]) < tau;
       if (tie) sc.flagged[atomicAdd(&sc.n_flagged, 1u)] = (uint32_t)etid;
     }
@@ -1079,23 +1089,31 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
-// Writes one 32-row x 64-byte chunk held as 16 packed words per thread (thread
-// = row) through the warp's staging buffer so that every global store
-// instruction covers 8 rows x 64 contiguous bytes instead of 32 rows x 16.
-// dst[i] / ok[i] describe row (lane >> 2) + 8 i: pointer to the chunk's first
-// byte in global memory and whether the row exists.
-__device__ __forceinline__ void store_chunk_coalesced(uint8_t* st, int lane, const uint32_t (&o)[16],
-                                                      uint8_t* const (&dst)[4], const bool (&ok)[4]) {
-  uint4* mine = reinterpret_cast<uint4*>(st + lane * 80);
+// Epilogue stores go through a per-warp staging buffer of 32 rows x 128 bytes so that every global
+// store instruction covers 4 rows x 128 contiguous bytes (whole cache lines; over NVLink, packets of
+// 128 bytes) instead of 32 rows x 16.  The thread that owns row r of the accumulator quadrant puts
+// its packed words into row r of the buffer; the 16-byte chunk c of a row sits at chunk c ^ (r & 7),
+// which keeps both the row-wise writes and the line-wise reads free of bank conflicts.
+__device__ __forceinline__ void stage_half_row(uint8_t* st, int lane, int half, const uint32_t (&o)[16]) {
 #pragma unroll
-  for (int v = 0; v < 4; ++v) mine[v] = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+  for (int v = 0; v < 4; ++v) {
+    const int c = half * 4 + v;
+    *reinterpret_cast<uint4*>(st + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+        make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+  }
+}
+
+// Stores the staged 32 x 128-byte block: lane l writes chunk (l & 7) of rows (l >> 3) + 4 i.
+// `myptr`: this lane's row pointer (first byte of its 128-byte segment in global memory), 0 = no row.
+__device__ __forceinline__ void store_staged_rows(uint8_t* st, int lane, unsigned long long myptr) {
   __syncwarp();
-  const int piece = lane & 3;
+  const int c = lane & 7;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int r = (lane >> 2) + 8 * i;
-    const uint4 val = *reinterpret_cast<const uint4*>(st + r * 80 + piece * 16);
-    if (ok[i]) *reinterpret_cast<uint4*>(dst[i] + piece * 16) = val;
+  for (int i = 0; i < 8; ++i) {
+    const int r = (lane >> 3) + 4 * i;
+    const unsigned long long pp = __shfl_sync(0xffffffffu, myptr, r);
+    const uint4 val = *reinterpret_cast<const uint4*>(st + r * 128 + ((c ^ (r & 7)) << 4));
+    if (pp != 0ull) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(pp) + (c << 4)) = val;
   }
   __syncwarp();
 }
@@ -1105,16 +1123,12 @@ __device__ __forceinline__ void ffn1_epilogue(const FdmoeParams& p, SmemCtl& sc,
                                               int lane, int ewarp, uint32_t e, uint32_t j, uint32_t n,
                                               uint32_t rows) {
   uint8_t* st = sc.store_stage[ewarp];
-  uint8_t* dst[4];
-  bool ok[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint32_t r = q * 32 + (lane >> 2) + 8 * i;
-    ok[i] = r < rows;
-    dst[i] = reinterpret_cast<uint8_t*>(reinterpret_cast<bf16*>(p.act) +
-                                        ((size_t)e * p.cap_rows + (size_t)j * 128 + r) * p.I +
-                                        n * FDMOE_TILE_N1 + h * 64);
-  }
+  const uint32_t row = q * 32 + lane;
+  unsigned long long myptr = 0ull;
+  if (row < rows)
+    myptr = reinterpret_cast<unsigned long long>(reinterpret_cast<bf16*>(p.act) +
+                                                 ((size_t)e * p.cap_rows + (size_t)j * 128 + row) * p.I +
+                                                 n * FDMOE_TILE_N1 + h * 64);
   const uint32_t tbase = taddr + ((uint32_t)(q * 32) << 16) + h * 64;
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
@@ -1122,16 +1136,13 @@ __device__ __forceinline__ void ffn1_epilogue(const FdmoeParams& p, SmemCtl& sc,
     ptx::tmem_ld_32x32(tbase + c * 32, g);
     ptx::tmem_ld_32x32(tbase + 128 + c * 32, u);
     ptx::tmem_ld_wait();
-    prof_mark(p, sc, ewarp * 32 + lane, 10 + c * 3);
 #pragma unroll
     for (int w = 0; w < 16; ++w)
       o[w] = pack_bf16(silu_mul(__uint_as_float(g[2 * w]), __uint_as_float(u[2 * w])),
                        silu_mul(__uint_as_float(g[2 * w + 1]), __uint_as_float(u[2 * w + 1])));
-    uint8_t* d2[4] = {dst[0] + c * 64, dst[1] + c * 64, dst[2] + c * 64, dst[3] + c * 64};
-    prof_mark(p, sc, ewarp * 32 + lane, 11 + c * 3);
-    store_chunk_coalesced(st, lane, o, d2, ok);
-    prof_mark(p, sc, ewarp * 32 + lane, 12 + c * 3);
+    stage_half_row(st, lane, c, o);
   }
+  store_staged_rows(st, lane, myptr);
 }
 
 // FFN2 epilogue: y[token, slot, n*256 + c] = D[row, c] * routing weight, stored
@@ -1152,25 +1163,20 @@ __device__ __forceinline__ bool ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc,
     myptr = reinterpret_cast<unsigned long long>(reinterpret_cast<bf16*>(p.peers[home].ystage) +
                                                  ((size_t)token * p.K + slot) * p.H + n * FDMOE_TILE_N2 + h * 128);
   }
-  uint8_t* dst[4];
-  bool ok[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const unsigned long long pp = __shfl_sync(0xffffffffu, myptr, (lane >> 2) + 8 * i);
-    dst[i] = reinterpret_cast<uint8_t*>(pp);
-    ok[i] = pp != 0ull;
-  }
   const uint32_t tbase = taddr + ((uint32_t)(q * 32) << 16) + h * 128;
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    uint32_t d[32], o[16];
-    ptx::tmem_ld_32x32(tbase + c * 32, d);
-    ptx::tmem_ld_wait();
+  for (int pass = 0; pass < 2; ++pass) {
 #pragma unroll
-    for (int w = 0; w < 16; ++w)
-      o[w] = pack_bf16(__uint_as_float(d[2 * w]) * wgt, __uint_as_float(d[2 * w + 1]) * wgt);
-    uint8_t* d2[4] = {dst[0] + c * 64, dst[1] + c * 64, dst[2] + c * 64, dst[3] + c * 64};
-    store_chunk_coalesced(st, lane, o, d2, ok);
+    for (int c = 0; c < 2; ++c) {
+      uint32_t d[32], o[16];
+      ptx::tmem_ld_32x32(tbase + (pass * 2 + c) * 32, d);
+      ptx::tmem_ld_wait();
+#pragma unroll
+      for (int w = 0; w < 16; ++w)
+        o[w] = pack_bf16(__uint_as_float(d[2 * w]) * wgt, __uint_as_float(d[2 * w + 1]) * wgt);
+      stage_half_row(st, lane, c, o);
+    }
+    store_staged_rows(st, lane, myptr ? myptr + (unsigned long long)(pass * 128) : 0ull);
   }
   return remote;
 }
@@ -1247,10 +1253,11 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
     st_relaxed<false>(&ctl->tokens_launch, (uint32_t)p.T);
   }
   {
-    static_assert(sizeof(FdmoeParams) % 16 == 0, "parameter block is copied in 16-byte pieces");
-    const uint4* src = reinterpret_cast<const uint4*>(&p);
-    uint4* dst = reinterpret_cast<uint4*>(&sc.params);
-    for (int i = tid; i < (int)(sizeof(FdmoeParams) / 16); i += kThreads) dst[i] = src[i];
+    static_assert(sizeof(FdmoeParams) % 16 == 0 && offsetof(FdmoeParams, peers) % 16 == 0,
+                  "parameter block is copied in 16-byte pieces");
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(&p) + offsetof(FdmoeParams, peers));
+    uint4* dst = reinterpret_cast<uint4*>(sc.params_tail);
+    for (int i = tid; i < (int)(sizeof(sc.params_tail) / 16); i += kThreads) dst[i] = src[i];
   }
   if (warp == kWarpTmem) {
     ptx::tmem_alloc(&sc.tmem_base, kTmemCols);
@@ -1335,7 +1342,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       uint32_t stage_it = 0;
       for (uint32_t it = 0;; ++it) {
         const uint32_t r = it % kRing, ph = (it / kRing) & 1u;
-        if (!wait_bar(p, sc, &sc.ring_full[r], ph, FDMOE_ERR_TIMEOUT_RING)) break;
+        if (!wait_bar(p, sc, &sc.ring_full[r], ph, FDMOE_ERR_TIMEOUT_RING, 2u)) break;
         const FdmoeSlot t = sc.ring[r];
         const uint32_t kind = t.a & 0xffu;
         if (kind == FDMOE_TASK_EXIT) break;
@@ -1436,7 +1443,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       uint32_t stage_it = 0, tile_it = 0, skips = 0;
       for (uint32_t it = 0;; ++it) {
         const uint32_t r = it % kRing, ph = (it / kRing) & 1u;
-        if (!wait_bar(p, sc, &sc.ring_full[r], ph, FDMOE_ERR_TIMEOUT_RING)) break;
+        if (!wait_bar(p, sc, &sc.ring_full[r], ph, FDMOE_ERR_TIMEOUT_RING, 2u)) break;
         const FdmoeSlot t = sc.ring[r];
         const uint32_t kind = t.a & 0xffu;
         if (kind == FDMOE_TASK_EXIT) break;
@@ -1511,7 +1518,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
       const uint32_t r = it % kRing, ph = (it / kRing) & 1u;
       // the group leaves together: a lone warp breaking out would strand the
       // others at the next group barrier
-      if (!epi_vote_all(wait_bar(p, sc, &sc.ring_full[r], ph, FDMOE_ERR_TIMEOUT_RING))) break;
+      if (!epi_vote_all(wait_bar(p, sc, &sc.ring_full[r], ph, FDMOE_ERR_TIMEOUT_RING, 2u))) break;
       const FdmoeSlot t = sc.ring[r];
       const uint32_t kind = t.a & 0xffu;
       if (kind == FDMOE_TASK_EXIT) break;
@@ -1525,15 +1532,15 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         if (!epi_vote_all(wait_bar(p, sc, &sc.tmem_full[acc], aph, FDMOE_ERR_TIMEOUT_TMEM))) break;
         if (p.prof && etid == 0) pt1 = prof_now();
         ptx::tcgen05_fence_after();
-        gate_epilogue<S>(sc.params, sc, tmem_base + acc * kAccCols, &sc.tmem_empty[acc], q, h, lane, etid, ewarp, j);
+        gate_epilogue<S>(task_params(sc), sc, tmem_base + acc * kAccCols, &sc.tmem_empty[acc], q, h, lane, etid, ewarp, j);
       } else if (kind == FDMOE_TASK_DISPATCH) {
-        if (!dispatch_task<S>(sc.params, sc, stage, stage_it, etid, ewarp, lane, j, rows)) break;
+        if (!dispatch_task<S>(task_params(sc), sc, stage, stage_it, etid, ewarp, lane, j, rows)) break;
         if (etid == 0) {
           __threadfence_block();
           sc.skip_done = sc.skip_done + 1u;
         }
       } else if (kind == FDMOE_TASK_GATEFIX) {
-        if (!gatefix_task<S>(sc.params, sc, stage, stage_it, etid, ewarp, lane, j, rows)) break;
+        if (!gatefix_task<S>(task_params(sc), sc, stage, stage_it, etid, ewarp, lane, j, rows)) break;
         if (etid == 0) {
           __threadfence_block();
           sc.skip_done = sc.skip_done + 1u;
@@ -1620,7 +1627,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
           maybe_close(p);
         }
       } else if (kind == FDMOE_TASK_GATED) {
-        gated_task<S>(sc.params, sc, etid);
+        gated_task<S>(task_params(sc), sc, etid);
       } else if (kind == FDMOE_TASK_TESTA || kind == FDMOE_TASK_TESTB) {
         // task-system self test: two dependent stages over a 256-element chunk
         int* ptr = p.test_buf + (size_t)j * kEpiThreads + etid;
@@ -1649,7 +1656,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
         epi_bar();
         if (r2) {
           if (etid == 0) sc.run_round2 = 0u;
-          gated_task<S>(sc.params, sc, etid);
+          gated_task<S>(task_params(sc), sc, etid);
         }
       }
       if (p.mode == 2) {

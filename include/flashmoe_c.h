@@ -85,6 +85,13 @@ int FlashMoeTestTaskSystem(FlashMoeHandle h, int32_t* data, int n, void* stream)
 int FlashMoeTestQueueGemm(FlashMoeHandle h, const uint32_t* rowsPerExpertHost, const void* A,
                           void* out, void* stream);
 
+/* Test hook for the device-side time-outs (the reference has no counterpart: its device waits are
+ * unbounded, src/hip/taskSystem/taskManager.h:208-215): a launch that expects one task nobody ever
+ * publishes.  Every worker's wait for work runs out after FLASHMOE_TIMEOUT_MS, the kernel records
+ * status 1 (a worker found no work for too long) and returns; the context stays usable, the launcher
+ * refuses further launches until it is destroyed and created again.  Nothing faults or hangs. */
+int FlashMoeTestStall(FlashMoeHandle h, void* stream);
+
 /* The whole layer in one call that allocates nothing (no counterpart in the reference, whose
  * launcher always allocates its scratch in Init, src/hip/launcher/moeKernelLauncher.hip:139-165).
  * For callers that may not touch the device allocator: an engine that has frozen its memory pool,

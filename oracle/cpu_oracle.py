@@ -59,6 +59,9 @@ class PortOracle:
         L.oracle_full_moe.argtypes = [_f32p, _f32p, _f32p, _f32p] + [C.c_int] * 5 + [
             _f32p, C.POINTER(C.c_float), C.POINTER(C.c_int), C.POINTER(C.c_float),
             C.POINTER(C.c_float), C.c_int]
+        _u16p = np.ctypeslib.ndpointer(dtype=np.uint16, flags="C_CONTIGUOUS")
+        L.oracle_full_moe_bw.argtypes = [_f32p, _f32p, _u16p, _u16p] + [C.c_int] * 5 + [
+            _f32p, C.POINTER(C.c_float), C.POINTER(C.c_int), C.c_int]
         L.oracle_rand_uniform_fill.argtypes = [_f32p, C.c_size_t, C.c_float, C.c_float, C.c_int]
         L.oracle_max_threads.restype = C.c_int
 
@@ -117,6 +120,20 @@ class PortOracle:
         self.lib.oracle_full_moe(tokens, gate_w, w13, w2, T, E, H, topk, I, out,
                                  _ptr(tw), _ptr(ti, C.c_int), _ptr(act), _ptr(y), threads)
         return out, tw, ti, act, y
+
+    def full_moe_bf16_weights(self, tokens, gate_w, w13_bits, w2_bits, topk: int, threads: int = 1):
+        """The layer with the expert weights given as bf16 bit patterns (uint16 arrays [E,2I,H] and
+        [E,H,I], e.g. a memory map shared between processes).  Returns (out, topk_w, topk_idx); equal
+        bit for bit to full_moe on the widened weights."""
+        T, H = tokens.shape
+        E = gate_w.shape[0]
+        I = w2_bits.shape[2]
+        out = np.zeros((T, H), np.float32)
+        tw = np.zeros((T, topk), np.float32)
+        ti = np.zeros((T, topk), np.int32)
+        self.lib.oracle_full_moe_bw(tokens, gate_w, w13_bits, w2_bits, T, E, H, topk, I, out, _ptr(tw),
+                                    _ptr(ti, C.c_int), threads)
+        return out, tw, ti
 
     def rand_uniform(self, n: int, lo: float, hi: float, reseed: bool) -> np.ndarray:
         out = np.empty(n, np.float32)

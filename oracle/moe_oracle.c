@@ -44,6 +44,33 @@ void oracle_gemm_nt(const float* A, const float* B, float* C, int M, int N,
   }
 }
 
+/* Same GEMM with B stored as bf16 (the upper 16 bits of the fp32 value).  A bf16 value
+ * widens to fp32 exactly, so the result equals oracle_gemm_nt on the widened B bit for bit;
+ * the benchmark's multi-rank parity check uses it to share one bf16 copy of all expert
+ * weights between the ranks instead of an fp32 copy per rank. */
+static float bf16_bits_to_f32(unsigned short b) {
+  union {
+    unsigned int u;
+    float f;
+  } v;
+  v.u = (unsigned int)b << 16;
+  return v.f;
+}
+
+void oracle_gemm_nt_bw(const float* A, const unsigned short* B, float* C, int M, int N,
+                       int K) {
+  for (int i = 0; i < M; ++i) {
+    const float* a = A + (size_t)i * (size_t)K;
+    float* c = C + (size_t)i * (size_t)N;
+    for (int j = 0; j < N; ++j) {
+      const unsigned short* b = B + (size_t)j * (size_t)K;
+      float acc = 0.0f;
+      for (int k = 0; k < K; ++k) acc += a[k] * bf16_bits_to_f32(b[k]);
+      c[j] = acc;
+    }
+  }
+}
+
 /* Per-row top-k by insertion: descending values, strict '>' so that among
  * equal values the lower column index stays first.
  * Follows test/singleGPU/cpp/moe/reference/refTopk.h:17-67. */
@@ -135,10 +162,13 @@ static float sigmoid_stable(float x) {
 /* out[rows,I] = silu(x W1^T) * (x W3^T) with W13 = [2I,H]: rows 0..I-1 are the
  * gate projection (left half of the GEMM output), rows I..2I-1 the up
  * projection.  Follows refExpertFFN1.h:31-48 (refSiluMul) and :51-65. */
-void oracle_ffn1(const float* tokens, const float* w13, int rows, int H, int I,
-                 float* out) {
+static void ffn1_any(const float* tokens, const void* w13, int wbf16, int rows, int H, int I,
+                     float* out) {
   float* g = (float*)malloc((size_t)rows * 2u * (size_t)I * sizeof(float));
-  oracle_gemm_nt(tokens, w13, g, rows, 2 * I, H);
+  if (wbf16)
+    oracle_gemm_nt_bw(tokens, (const unsigned short*)w13, g, rows, 2 * I, H);
+  else
+    oracle_gemm_nt(tokens, (const float*)w13, g, rows, 2 * I, H);
   for (int r = 0; r < rows; ++r) {
     const float* a = g + (size_t)r * 2u * (size_t)I;
     const float* b = a + I;
@@ -151,10 +181,15 @@ void oracle_ffn1(const float* tokens, const float* w13, int rows, int H, int I,
   free(g);
 }
 
+void oracle_ffn1(const float* tokens, const float* w13, int rows, int H, int I,
+                 float* out) {
+  ffn1_any(tokens, w13, 0, rows, H, I, out);
+}
+
 /* One token through gate-selected experts; stage buffers are optional.
  * act_out [K,I]: SwiGLU activations per slot; y_out [K,H]: unscaled FFN2 rows.
  * Follows refFullMoe.h:36-66 (the body of the per-token loop). */
-static void moe_one_token(const float* x, const float* w13, const float* w2,
+static void moe_one_token(const float* x, const void* w13, const void* w2, int wbf16,
                           const float* gate_scores, const int* experts, int E,
                           int H, int topk, int I, float* out, float* act_out,
                           float* y_out, float* act_tmp, float* y_tmp) {
@@ -169,16 +204,22 @@ static void moe_one_token(const float* x, const float* w13, const float* w2,
       if (y_out) memset(y, 0, (size_t)H * sizeof(float));
       continue;
     }
-    const float* w13e = w13 + (size_t)e * (size_t)H * (size_t)(2 * I);
-    const float* w2e = w2 + (size_t)e * (size_t)H * (size_t)I;
-    oracle_ffn1(x, w13e, 1, H, I, act);
-    oracle_gemm_nt(act, w2e, y, 1, H, I);
+    const size_t esz = wbf16 ? 2u : 4u;
+    const char* w13e = (const char*)w13 + (size_t)e * (size_t)H * (size_t)(2 * I) * esz;
+    const char* w2e = (const char*)w2 + (size_t)e * (size_t)H * (size_t)I * esz;
+    ffn1_any(x, w13e, wbf16, 1, H, I, act);
+    if (wbf16)
+      oracle_gemm_nt_bw(act, (const unsigned short*)w2e, y, 1, H, I);
+    else
+      oracle_gemm_nt(act, (const float*)w2e, y, 1, H, I);
     for (int d = 0; d < H; ++d) out[d] += y[d] * score;
   }
 }
 
 typedef struct {
-  const float *tokens, *w13, *w2, *tw;
+  const float *tokens, *tw;
+  const void *w13, *w2;
+  int wbf16;
   const int* ti;
   float *out, *act_out, *y_out;
   int T, E, H, topk, I;
@@ -192,7 +233,7 @@ static void* moe_worker(void* arg) {
   float* y_tmp = (float*)malloc((size_t)j->H * sizeof(float));
   for (int t = j->tid; t < j->T; t += j->nthreads) {
     moe_one_token(
-        j->tokens + (size_t)t * (size_t)j->H, j->w13, j->w2,
+        j->tokens + (size_t)t * (size_t)j->H, j->w13, j->w2, j->wbf16,
         j->tw + (size_t)t * (size_t)j->topk, j->ti + (size_t)t * (size_t)j->topk,
         j->E, j->H, j->topk, j->I, j->out + (size_t)t * (size_t)j->H,
         j->act_out ? j->act_out + (size_t)t * (size_t)j->topk * (size_t)j->I : NULL,
@@ -208,10 +249,10 @@ static void* moe_worker(void* arg) {
  * act_out [T,K,I], y_out [T,K,H] (any may be NULL).  `threads` > 1 splits the
  * independent token loop over that many POSIX threads; results do not depend
  * on it.  Follows test/singleGPU/cpp/moe/reference/refFullMoe.h:9-69. */
-void oracle_full_moe(const float* tokens, const float* gate_w, const float* w13,
-                     const float* w2, int T, int E, int H, int topk, int I,
-                     float* out, float* topk_w_out, int* topk_idx_out,
-                     float* act_out, float* y_out, int threads) {
+static void full_moe_any(const float* tokens, const float* gate_w, const void* w13,
+                         const void* w2, int wbf16, int T, int E, int H, int topk, int I,
+                         float* out, float* topk_w_out, int* topk_idx_out,
+                         float* act_out, float* y_out, int threads) {
   if (T <= 0) return;
   float* tw = topk_w_out ? topk_w_out
                          : (float*)malloc((size_t)T * (size_t)topk * sizeof(float));
@@ -223,8 +264,8 @@ void oracle_full_moe(const float* tokens, const float* gate_w, const float* w13,
   moe_job_t* jobs = (moe_job_t*)malloc((size_t)threads * sizeof(moe_job_t));
   pthread_t* th = (pthread_t*)malloc((size_t)threads * sizeof(pthread_t));
   for (int i = 0; i < threads; ++i) {
-    moe_job_t j = {tokens, w13, w2, tw, ti, out, act_out, y_out,
-                   T,      E,   H,  topk, I, i,  threads};
+    moe_job_t j = {tokens, tw, w13, w2, wbf16, ti, out, act_out, y_out,
+                   T,      E,  H,   topk, I,    i,  threads};
     jobs[i] = j;
   }
   for (int i = 1; i < threads; ++i) pthread_create(&th[i], NULL, moe_worker, &jobs[i]);
@@ -234,6 +275,23 @@ void oracle_full_moe(const float* tokens, const float* gate_w, const float* w13,
   free(th);
   if (!topk_w_out) free(tw);
   if (!topk_idx_out) free(ti);
+}
+
+void oracle_full_moe(const float* tokens, const float* gate_w, const float* w13,
+                     const float* w2, int T, int E, int H, int topk, int I,
+                     float* out, float* topk_w_out, int* topk_idx_out,
+                     float* act_out, float* y_out, int threads) {
+  full_moe_any(tokens, gate_w, w13, w2, 0, T, E, H, topk, I, out, topk_w_out, topk_idx_out, act_out,
+               y_out, threads);
+}
+
+/* The full layer with the expert weights stored as bf16 (see oracle_gemm_nt_bw): same results
+ * as oracle_full_moe on the widened weights. */
+void oracle_full_moe_bw(const float* tokens, const float* gate_w, const unsigned short* w13,
+                        const unsigned short* w2, int T, int E, int H, int topk, int I,
+                        float* out, float* topk_w_out, int* topk_idx_out, int threads) {
+  full_moe_any(tokens, gate_w, w13, w2, 1, T, E, H, topk, I, out, topk_w_out, topk_idx_out, NULL, NULL,
+               threads);
 }
 
 /* Host cores available to this process. */

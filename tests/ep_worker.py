@@ -27,10 +27,17 @@ def main():
     case = sys.argv[4]
     counts = [int(v) for v in sys.argv[5:5 + world]]
     torch.cuda.set_device(rank)
-    shape = synth.TINY if case.startswith("tiny") else synth.QWEN3_30B_A3B
+    shape = (synth.TINY if case.startswith("tiny") else
+             synth.QWEN3_235B_E16 if case.startswith("q235") else synth.QWEN3_30B_A3B)
     std = 0.05 if shape is synth.TINY else 0.02
     gate, w13, w2 = synth.make_weights(shape, seed=11, std=std)
     xs = [synth.make_tokens(shape, n, seed=100 + r) for r, n in enumerate(counts)]
+    if case.endswith("zipf"):
+        # the fourth benchmark configuration's routing: the most popular experts take a row from every
+        # token of every rank, so their buffers on the owning rank are filled to exactly their capacity
+        allx = torch.cat(xs)
+        gate, allx, _ = synth.zipf_routing(shape, gate, allx)
+        xs = list(torch.split(allx, counts))
     if case.endswith("local"):
         # the reference's forced routing (test/common/moeTools.h:187-207): token t is a one-hot at
         # column t and its K experts get gate weight 100 there, all inside one rank's shard
@@ -46,7 +53,8 @@ def main():
                 col += 1
     el = shape.experts // world
     layer = tl.GpuLayer(shape, gate, w13[rank * el:(rank + 1) * el].contiguous(),
-                        w2[rank * el:(rank + 1) * el].contiguous(), max_tokens=max(counts) + 2,
+                        w2[rank * el:(rank + 1) * el].contiguous(),
+                        max_tokens=counts[rank] if case.endswith("zipf") else max(counts) + 2,
                         rank=rank, world=world, uid=uid, device=f"cuda:{rank}")
     port = cpu_oracle.PortOracle()
     ok = True

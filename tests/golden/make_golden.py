@@ -48,6 +48,12 @@ def main():
     x, gate, w13, w2 = tl.reference_stream_inputs(48)
     np.savez_compressed(os.path.join(HERE, "qwen3_30b_t48_refstream.npz"),
                         **run_ref(ref, x, gate, w13, w2, 8, threads))
+    # 4. Qwen3-235B-A22B hidden/intermediate sizes with 16 experts (one rank's share at 8 GPUs), 24 tokens
+    s = synth.QWEN3_235B_E16
+    gate, w13, w2 = synth.make_weights(s, seed=5)
+    x = synth.make_tokens(s, 24, seed=5)
+    np.savez_compressed(os.path.join(HERE, "qwen3_235b_e16_t24_seed5.npz"),
+                        **run_ref(ref, x, gate, w13, w2, s.topk, threads))
     print("golden vectors written to", HERE)
 
 

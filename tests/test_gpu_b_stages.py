@@ -18,6 +18,27 @@ from moe_testlib import cpu_oracle, synth
 pytestmark = pytest.mark.gpu
 
 
+def check_routing_and_output(shape, x, gate, w13, w2, max_tokens):
+    """Top-k indices (exact, in order), routing weights and the output of one launch against the oracle,
+    without pulling the row buffers: for token counts whose stage buffers run to gigabytes."""
+    port = cpu_oracle.PortOracle()
+    T, K = x.shape[0], shape.topk
+    o_out, o_w, o_idx, _, _ = port.full_moe(tl.f32(x), tl.f32(gate), tl.f32(w13), tl.f32(w2), K,
+                                            threads=port.max_threads(), stages=True)
+    layer = tl.GpuLayer(shape, gate, w13, w2, max_tokens)
+    try:
+        out = tl.f32(layer.run(x))
+        idx = np.frombuffer(layer.launcher.debug_read(0, T * K * 4), np.int32).reshape(T, K)
+        w = np.frombuffer(layer.launcher.debug_read(1, T * K * 4), np.float32).reshape(T, K)
+        cnt = np.frombuffer(layer.launcher.debug_read(2, layer.e_local * 4), np.uint32)
+    finally:
+        layer.close()
+    assert np.array_equal(idx, o_idx), f"top-k mismatch on {(idx != o_idx).any(1).sum()} tokens"
+    assert np.abs(w - o_w).max() <= 1e-5
+    assert np.array_equal(cnt, np.bincount(o_idx.ravel(), minlength=shape.experts))
+    tl.assert_close_bf16(out, o_out, "layer output")
+
+
 def check_layer(shape, x, gate, w13, w2, max_tokens, golden=None, inplace=False, check_stages=True):
     port = cpu_oracle.PortOracle()
     T = x.shape[0]
@@ -125,3 +146,42 @@ def test_zipf_skewed_routing():
     x = synth.make_tokens(s, 700, seed=4)
     gate, x = synth.add_zipf_bias(s, gate, x, s=1.2, scale=1.0, seed=4)
     check_layer(s, x, gate, w13, w2, max_tokens=700)
+
+
+def test_qwen3_235b_sizes_ragged_tokens():
+    # hidden 4096 / intermediate 1536: the exact gate path stages an 8 KB token row, a dispatch stage holds
+    # 6 rows instead of 12, COMBINE takes two passes over the hidden columns; 200 tokens, maxTokens above
+    s = synth.QWEN3_235B_E16
+    gate, w13, w2 = synth.make_weights(s, seed=5)
+    check_layer(s, synth.make_tokens(s, 200, seed=6), gate, w13, w2, max_tokens=208)
+
+
+def test_qwen3_235b_sizes_golden_24_tokens_in_place():
+    s = synth.QWEN3_235B_E16
+    gate, w13, w2 = synth.make_weights(s, seed=5)
+    check_layer(s, synth.make_tokens(s, 24, seed=5), gate, w13, w2, max_tokens=24,
+                golden="qwen3_235b_e16_t24_seed5.npz", inplace=True)
+
+
+def test_qwen3_235b_sizes_many_tiles_per_expert():
+    # 1100 tokens x 8 slots over 16 experts: about 550 rows, five m-tiles, per expert
+    s = synth.QWEN3_235B_E16
+    gate, w13, w2 = synth.make_weights(s, seed=5)
+    check_layer(s, synth.make_tokens(s, 1100, seed=7), gate, w13, w2, max_tokens=1100)
+
+
+def test_qwen3_30b_second_config_4096_tokens_routing_and_output():
+    # the benchmark's single-GPU configuration: all 4096 tokens, top-k exact for every one of them
+    s = synth.QWEN3_30B_A3B
+    gate, w13, w2 = synth.make_weights(s, seed=0)
+    check_routing_and_output(s, synth.make_tokens(s, 4096, seed=9), gate, w13, w2, max_tokens=4096)
+
+
+def test_qwen3_30b_zipf_routing_hottest_expert_takes_every_token():
+    # the fourth benchmark configuration's routing: the two most popular experts are selected by every
+    # token, so their row buffers are filled to exactly their capacity of one row per token
+    s = synth.QWEN3_30B_A3B
+    gate, w13, w2 = synth.make_weights(s, seed=0)
+    gate, x, info = synth.zipf_routing(s, gate, synth.make_tokens(s, 640, seed=10))
+    assert info["selection_share_realised_top8"][0] == 1.0
+    check_routing_and_output(s, x, gate, w13, w2, max_tokens=640)

@@ -55,8 +55,22 @@ def test_two_ranks_qwen3_30b_shape():
     run_ranks("qwen", [160, 96])
 
 
+def test_two_ranks_qwen3_235b_sizes():
+    # hidden 4096 / intermediate 1536 with 8 experts per rank
+    run_ranks("q235", [150, 70])
+
+
+def test_two_ranks_zipf_routing_buffers_exactly_full():
+    # maxTokens equals each rank's token count: the hottest experts' buffers hold exactly one row per token
+    run_ranks("qwen_zipf", [200, 184])
+
+
 def test_four_ranks_uneven_tokens():
     run_ranks("tiny", [3, 50, 0, 129])
+
+
+def test_four_ranks_qwen3_235b_sizes():
+    run_ranks("q235", [64, 0, 200, 33])
 
 
 def test_eight_ranks_qwen3_30b_shape():

@@ -124,3 +124,22 @@ def test_golden_qwen3_30b_first_config(port):
 def test_golden_reference_test_stream(port):
     x, gate, w13, w2 = tl.reference_stream_inputs(48)
     _check_golden(port, "qwen3_30b_t48_refstream.npz", x, gate, w13, w2, 8)
+
+
+def test_golden_qwen3_235b_sizes(port):
+    s = synth.QWEN3_235B_E16
+    gate, w13, w2 = synth.make_weights(s, seed=5)
+    _check_golden(port, "qwen3_235b_e16_t24_seed5.npz", synth.make_tokens(s, 24, seed=5), gate, w13, w2, s.topk)
+
+
+def test_bf16_weight_variant_equals_widened_weights(port):
+    # the variant the benchmark's multi-rank parity check uses (one bf16 copy of all expert weights
+    # shared between the ranks): bit-identical to the fp32 entry point on the widened weights
+    import torch
+    s = synth.TINY
+    gate, w13, w2 = synth.make_weights(s, seed=6, std=0.05)
+    x = tl.f32(synth.make_tokens(s, 33, seed=6))
+    out, tw, ti, _, _ = port.full_moe(x, tl.f32(gate), tl.f32(w13), tl.f32(w2), s.topk, threads=3, stages=True)
+    bits = lambda t: t.view(torch.int16).numpy().view(np.uint16)  # noqa: E731
+    out2, tw2, ti2 = port.full_moe_bf16_weights(x, tl.f32(gate), bits(w13), bits(w2), s.topk, threads=2)
+    assert np.array_equal(out, out2) and np.array_equal(tw, tw2) and np.array_equal(ti, ti2)

@@ -1,0 +1,100 @@
+"""The vLLM patch (twin of the reference's test/multiGPU/python/flash_moe_patch.py): the wrapper class
+around a block with vLLM's attribute layout, and the mechanism that applies the patch in every process
+of a job (a sitecustomize.py on PYTHONPATH plus an import hook)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import moe_testlib as tl
+from moe_testlib import cpu_oracle, synth
+from flash_distributed_moe_b200 import vllm_patch
+
+
+def _vllm_importable():
+    try:
+        import importlib.util
+        return importlib.util.find_spec("vllm") is not None
+    except Exception:
+        return False
+
+
+@pytest.mark.skipif(not _vllm_importable(), reason="vLLM is not installed")
+def test_patch_reaches_a_freshly_started_process():
+    # a process started after enable_flash_moe_patching() (as vLLM's spawned workers are) gets the
+    # wrapper class as soon as it imports vLLM's qwen3_moe module
+    code = (
+        "import sys; sys.path.insert(0, %r)\n"
+        "from flash_distributed_moe_b200.vllm_patch import enable_flash_moe_patching\n"
+        "import os, subprocess\n"
+        "os.environ.pop('FLASH_MOE_ENABLED', None)\n"
+        "import vllm.model_executor.models.qwen3_moe as q0\n"
+        "assert not getattr(q0.Qwen3MoeSparseMoeBlock, '_flash_moe_wrapper', False)\n"
+        "enable_flash_moe_patching()\n"
+        "assert q0.Qwen3MoeSparseMoeBlock._flash_moe_wrapper\n"
+        "child = 'import vllm.model_executor.models.qwen3_moe as q; "
+        "print(\"CHILD\", getattr(q.Qwen3MoeSparseMoeBlock, \"_flash_moe_wrapper\", False), "
+        "q.Qwen3MoeSparseMoeBlock.__mro__[1].__name__)'\n"
+        "print(subprocess.run([sys.executable, '-c', child], capture_output=True, text=True).stdout)\n"
+    ) % tl.ROOT
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert "CHILD True Qwen3MoeSparseMoeBlock" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+class _Experts(torch.nn.Module):
+    def __init__(self, w13, w2):
+        super().__init__()
+        self.w13_weight = torch.nn.Parameter(w13, requires_grad=False)
+        self.w2_weight = torch.nn.Parameter(w2, requires_grad=False)
+
+
+class _Cfg:
+    """The two attributes of vLLM's config object the wrapper reads."""
+
+    def __init__(self, topk):
+        self.model_config = type("M", (), {"hf_text_config": type("H", (), {"num_experts_per_tok": topk})()})()
+
+
+class _FakeBlock(torch.nn.Module):
+    """Stand-in with the attribute layout of vLLM's Qwen3MoeSparseMoeBlock on one rank."""
+    weights = None
+
+    def __init__(self, vllm_config, prefix=""):
+        super().__init__()
+        gate, w13, w2 = _FakeBlock.weights
+        self.gate = torch.nn.Linear(gate.shape[1], gate.shape[0], bias=False, dtype=gate.dtype, device=gate.device)
+        self.gate.weight = torch.nn.Parameter(gate, requires_grad=False)
+        self.experts = _Experts(w13, w2)
+        self.ep_group, self.ep_rank, self.ep_size = None, 0, 1
+        self.fallback_calls = 0
+
+    def forward(self, hidden_states):
+        self.fallback_calls += 1
+        return hidden_states
+
+
+@pytest.mark.gpu
+def test_wrapper_class_runs_the_layer_in_place_and_falls_back_above_max_tokens(monkeypatch):
+    s = synth.TINY
+    gate, w13, w2 = synth.make_weights(s, std=0.05)
+    _FakeBlock.weights = (gate.cuda(), w13.cuda(), w2.cuda())
+    monkeypatch.setenv("FLASH_MOE_MAX_TOKENS", "64")
+    wrapper = vllm_patch.make_wrapper_class(_FakeBlock)(_Cfg(s.topk))
+    port = cpu_oracle.PortOracle()
+    for batch in (1, 16, 64):
+        x = synth.make_tokens(s, batch, seed=40 + batch)
+        hidden = x.cuda()
+        got = wrapper(hidden)
+        torch.cuda.synchronize()
+        assert got.data_ptr() == hidden.data_ptr()
+        ref = port.full_moe(tl.f32(x), tl.f32(gate), tl.f32(w13), tl.f32(w2), s.topk)
+        tl.assert_close_bf16(tl.f32(got.cpu()), ref, f"wrapper, batch {batch}")
+    assert wrapper.fallback_calls == 0
+    wrapper(synth.make_tokens(s, 65).cuda())  # more tokens than the launcher takes: vLLM's own block
+    assert wrapper.fallback_calls == 1
+    wrapper.launcher.destroy()
+    wrapper.launcher = None
