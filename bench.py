@@ -55,7 +55,7 @@ def algorithmic_bytes(s, tokens, world) -> float:
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the persistent kernel from ncu, for the
 # workloads that were captured (profiles/): (shape, tokens per GPU, GPUs) -> bytes
-MEASURED_TRAFFIC = {}
+MEASURED_TRAFFIC = {("30b", 4096, 1): 1.637e9 + 0.328e9}
 
 
 def measured_peaks():
@@ -421,6 +421,24 @@ def main():
         expert_tflops = shape.topk * 6.0 * shape.hidden * shape.inter * T / (mean_launch_ms * 1e-3) / 1e12
         alg_bytes = algorithmic_bytes(shape, T, world)
         hbm_gbs = alg_bytes / (mean_launch_ms * 1e-3) / 1e9
+        # The launch has two floors: its expert GEMMs at the measured tensor peak and its algorithmic bytes
+        # at the measured copy bandwidth.  The bound reported is the higher floor (the larger fraction);
+        # both fractions are given.
+        tensor_frac = achieved_tflops / peaks["bf16_tflops"]
+        hbm_frac = hbm_gbs / peaks["hbm_gbs"]
+        roofline = {"kernel": "moe_persistent_kernel", "kernel_ms": mean_launch_ms,
+                    "peak_source": peaks["source"] + " (tensor: burst)",
+                    "tensor_tflops": achieved_tflops, "tensor_peak_tflops": peaks["bf16_tflops"], "tensor_frac": tensor_frac,
+                    "expert_gemm_tflops": expert_tflops, "expert_gemm_frac": expert_tflops / peaks["bf16_tflops"],
+                    "hbm_algorithmic_gbs": hbm_gbs, "hbm_peak_gbs": peaks["hbm_gbs"], "hbm_frac": hbm_frac,
+                    "algorithmic_bytes": alg_bytes, "algorithmic_flop": flop_launch,
+                    "traffic": MEASURED_TRAFFIC.get((args.shape, T, world)),
+                    "traffic_unit": "bytes/launch (ncu dram read+write)"}
+        if hbm_frac > tensor_frac:
+            roofline.update({"bound": "hbm", "achieved": hbm_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": hbm_frac})
+        else:
+            roofline.update({"bound": "tensor", "achieved": achieved_tflops, "peak": peaks["bf16_tflops"],
+                             "unit": "TFLOP/s", "frac": tensor_frac})
         config = {"workload": workload_name(shape, T, world, args.skew),
                   "hidden": shape.hidden, "inter": shape.inter, "tokens_per_gpu": T,
                   "l2_policy": "inputs larger than L2 (expert weights and row buffers touched per step exceed 126 MB)"}
@@ -431,15 +449,7 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": config,
-            "roofline": {"bound": "tensor", "achieved": achieved_tflops, "peak": peaks["bf16_tflops"],
-                         "unit": "TFLOP/s", "frac": achieved_tflops / peaks["bf16_tflops"],
-                         "expert_gemm_tflops": expert_tflops, "expert_gemm_frac": expert_tflops / peaks["bf16_tflops"],
-                         "traffic": MEASURED_TRAFFIC.get((args.shape, T, world)),
-                         "traffic_unit": "bytes/launch (ncu dram read+write)",
-                         "algorithmic_bytes": alg_bytes,
-                         "peak_source": peaks["source"] + " burst",
-                         "kernel": "moe_persistent_kernel", "kernel_ms": mean_launch_ms,
-                         "hbm_algorithmic_gbs": hbm_gbs, "hbm_frac_of_" + peaks["source"]: hbm_gbs / peaks["hbm_gbs"]},
+            "roofline": roofline,
             "e2e": {"value": tokens_total / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": int(h_in.numel() * 2), "d2h_bytes_per_step": int(h_out.numel() * 2),
                     "matches_device_path": bool(e2e_ok)},

@@ -1183,7 +1183,7 @@ __device__ __forceinline__ bool ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc,
 
 // COMBINE streams the K weighted rows of each token of a group through the
 // shared-memory stage ring with 1-D bulk copies (issued by the TMA warp) in
-// pieces of up to 2048 columns: stage layout [K][piece], 4 KB per slot row.
+// pieces of up to 2048 columns: stage layout [K][piece], the piece's bytes per slot row.
 constexpr int kCombineCols = 2048;
 
 // k-blocks a tile task puts into one pipeline stage: two for GATE tiles of up to 64 tokens
@@ -1425,9 +1425,13 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
               const uint32_t wbytes = (uint32_t)min(kCombineCols, p.H - c0) * 2u;
               uint8_t* sa = stage + s * kStageBytes;
               ptx::mbar_expect_tx(&sc.full_bar[s], wbytes * (uint32_t)p.K);
-              for (int k = 0; k < p.K; ++k)
-                ptx::bulk_load_1d(sa + k * (kCombineCols * 2), ys + ((size_t)tk * p.K + k) * p.H + c0, wbytes,
-                                  &sc.full_bar[s]);
+              if (p.H <= kCombineCols) {
+                // the K rows of a token are contiguous: one copy
+                ptx::bulk_load_1d(sa, ys + (size_t)tk * p.K * p.H, wbytes * (uint32_t)p.K, &sc.full_bar[s]);
+              } else {
+                for (int k = 0; k < p.K; ++k)
+                  ptx::bulk_load_1d(sa + k * wbytes, ys + ((size_t)tk * p.K + k) * p.H + c0, wbytes, &sc.full_bar[s]);
+              }
             }
           }
           if (!ok) break;
@@ -1596,7 +1600,7 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
 #pragma unroll
               for (int i = 0; i < 8; ++i) acc[i] = 0.f;
               for (int k = 0; k < p.K; ++k) {
-                const uint4 rr = sm[k * (kCombineCols / 8)];
+                const uint4 rr = sm[k * nvec];
                 const uint32_t w[4] = {rr.x, rr.y, rr.z, rr.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -1754,9 +1758,16 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
             // fence for the whole warp (the last m-tiles of a launch complete dozens of groups each).
             fence_acqrel<false>();
             uint32_t c_home[4], c_first[4], c_ntok[4], nc = 0u;
+            // (the four counter updates of a lane are issued back to back, their results are looked
+            // at afterwards: over NVLink each takes microseconds to answer)
+            uint32_t r_home[4], r_first[4], r_ntok[4], r_got[4];
 #pragma unroll
             for (uint32_t rr = 0; rr < 4u; ++rr) {
               const uint32_t r = rr * 32u + (uint32_t)lane;
+              r_home[rr] = 0xffffffffu;
+              r_first[rr] = 0u;
+              r_ntok[rr] = 0u;
+              r_got[rr] = 0u;
               c_home[rr] = 0u;
               c_first[rr] = 0u;
               c_ntok[rr] = 0u;
@@ -1765,23 +1776,27 @@ moe_persistent_kernel(const __grid_constant__ FdmoeParams p) {
                 const int hm = (int)mraw.y >> 8;
                 const uint32_t g = mraw.x / G;
                 const uint32_t th = tokens_of_rank(p, hm);
-                const uint32_t cnt = min(G, th - g * G);
-                uint32_t got;
+                r_home[rr] = (uint32_t)hm;
+                r_first[rr] = g * G;
+                r_ntok[rr] = min(G, th - g * G);
                 if (S && hm != p.rank)
-                  got = atom_add<true>(&p.peers[hm].grp_cnt[g], 1u) + 1u;
+                  r_got[rr] = atom_add<true>(&p.peers[hm].grp_cnt[g], 1u) + 1u;
                 else
-                  got = atom_add<false>(&p.peers[hm].grp_cnt[g], 1u) + 1u;
-                if (got == cnt * (uint32_t)p.K) {
+                  r_got[rr] = atom_add<false>(&p.peers[hm].grp_cnt[g], 1u) + 1u;
+              }
+            }
 #pragma unroll
-                  for (uint32_t c = 0; c < 4u; ++c) {
-                    if (c == nc) {
-                      c_home[c] = (uint32_t)hm;
-                      c_first[c] = g * G;
-                      c_ntok[c] = cnt;
-                    }
+            for (uint32_t rr = 0; rr < 4u; ++rr) {
+              if (r_home[rr] != 0xffffffffu && r_got[rr] == r_ntok[rr] * (uint32_t)p.K) {
+#pragma unroll
+                for (uint32_t c = 0; c < 4u; ++c) {
+                  if (c == nc) {
+                    c_home[c] = r_home[rr];
+                    c_first[c] = r_first[rr];
+                    c_ntok[c] = r_ntok[rr];
                   }
-                  ++nc;
                 }
+                ++nc;
               }
             }
             uint32_t ticket[4];

@@ -10,10 +10,13 @@ environment variable FLASH_MOE_ENABLED=1 is set.  Differences from the reference
     own block there (flash_moe_patch.py:104), this kernel dispatches rows to the experts' owners
     itself.  The unique id travels over `torch.distributed.broadcast_object_list` in the EP group,
     as in the reference (flash_moe_patch.py:73-87);
-  * the launcher is created at the first forward call, when the weights have been loaded and
-    post-processed, and vLLM's weight post-processing is left alone (the reference turns it into a
-    no-op); the expert weights must be in vLLM's canonical layout `[experts/ep, 2*inter, hidden]`
-    (gate projection rows first) and `[experts/ep, hidden, inter]`, bf16 or fp32;
+  * the launcher is created at the first forward call, when the weights have been loaded.  It needs
+    the expert weights in vLLM's canonical layout `[experts/ep, 2*inter, hidden]` (gate projection
+    rows first) and `[experts/ep, hidden, inter]`, bf16 or fp32.  vLLM's weight post-processing may
+    re-block them for its own kernels (on B200, vLLM 0.22 turns `[32, 256, 256]` into
+    `[32, 4, 256, 64]`), so the patch keeps a copy in the canonical layout, taken just before that
+    step, while leaving the step itself alone (the reference turns it into a no-op, which would
+    break vLLM's own path for batches above the token bound);
   * `FLASH_MOE_MAX_TOKENS` (default 8192) bounds the tokens per call that go through the kernel;
     larger batches use vLLM's block, like the reference's `num_tokens < maxTokens` test.
 
@@ -53,8 +56,10 @@ def make_wrapper_class(base):
 
         def _create_launcher(self) -> None:
             gate_w = self.gate.weight
-            w13 = self.experts.w13_weight
-            w2 = self.experts.w2_weight
+            w13 = getattr(self.experts, "_flash_moe_w13", None)
+            w2 = getattr(self.experts, "_flash_moe_w2", None)
+            if w13 is None or w2 is None:
+                w13, w2 = self.experts.w13_weight, self.experts.w2_weight
             experts, hidden = gate_w.shape
             inter = w2.shape[2]
             if (tuple(w13.shape) != (experts // self.ep_size, 2 * inter, hidden) or not w13.is_contiguous()
@@ -106,6 +111,22 @@ def apply_flash_moe_patch() -> bool:
         wrapper = make_wrapper_class(qwen3_moe.Qwen3MoeSparseMoeBlock)
         wrapper._flash_moe_wrapper = True
         qwen3_moe.Qwen3MoeSparseMoeBlock = wrapper
+    try:
+        # keep the expert weights in their canonical layout before vLLM re-blocks them
+        from vllm.model_executor.layers.fused_moe import UnquantizedFusedMoEMethod as method
+        if not getattr(method.process_weights_after_loading, "_flash_moe_wrapped", False):
+            original = method.process_weights_after_loading
+
+            def process_weights_after_loading(self, layer):
+                if hasattr(layer, "w13_weight") and hasattr(layer, "w2_weight"):
+                    layer._flash_moe_w13 = layer.w13_weight.data.clone().contiguous()
+                    layer._flash_moe_w2 = layer.w2_weight.data.clone().contiguous()
+                return original(self, layer)
+
+            process_weights_after_loading._flash_moe_wrapped = True
+            method.process_weights_after_loading = process_weights_after_loading
+    except Exception as e:
+        print(f"[PID {os.getpid()}] FlashMoE patch: expert weights are not copied before post-processing: {e}")
     _PATCHED = True
     return True
 
