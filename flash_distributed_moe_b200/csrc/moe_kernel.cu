@@ -1164,6 +1164,10 @@ __device__ __forceinline__ bool ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc,
                                                  ((size_t)token * p.K + slot) * p.H + n * FDMOE_TILE_N2 + h * 128);
   }
   const uint32_t tbase = taddr + ((uint32_t)(q * 32) << 16) + h * 128;
+  // Rows that go to another GPU may leave as bulk copies (one 128-byte copy per row and pass, issued by
+  // the row's lane from a linear staging row): the copy engine keeps more writes in flight over NVLink
+  // than the SM's store path does.
+  const bool bulk = p.bulk_return != 0 && __any_sync(0xffffffffu, remote);
 #pragma unroll
   for (int pass = 0; pass < 2; ++pass) {
 #pragma unroll
@@ -1174,10 +1178,25 @@ __device__ __forceinline__ bool ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc,
 #pragma unroll
       for (int w = 0; w < 16; ++w)
         o[w] = pack_bf16(__uint_as_float(d[2 * w]) * wgt, __uint_as_float(d[2 * w + 1]) * wgt);
-      stage_half_row(st, lane, c, o);
+      if (bulk) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+          *reinterpret_cast<uint4*>(st + lane * 128 + ((c * 4 + v) << 4)) =
+              make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+      } else {
+        stage_half_row(st, lane, c, o);
+      }
     }
-    store_staged_rows(st, lane, myptr ? myptr + (unsigned long long)(pass * 128) : 0ull);
+    if (bulk) {
+      ptx::fence_proxy_async();  // the staged row (generic writes) before the copy engine reads it
+      if (myptr) ptx::bulk_store_1d(reinterpret_cast<uint8_t*>(myptr) + pass * 128, st + lane * 128, 128u);
+      ptx::bulk_commit_group();
+      ptx::bulk_wait_group_read0();  // the staging row may be overwritten
+    } else {
+      store_staged_rows(st, lane, myptr ? myptr + (unsigned long long)(pass * 128) : 0ull);
+    }
   }
+  if (bulk) ptx::bulk_wait_group0();  // the rows are written before the tile is handed on
   return remote;
 }
 
