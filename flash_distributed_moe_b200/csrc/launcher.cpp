@@ -339,7 +339,6 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
   // publication batch (0 = chosen per launch from the token counts).
   params_.disp_conc = std::max(0, EnvInt("FLASHMOE_DISPATCH_WORKERS", 0));
   params_.batch_mt = std::max(0, EnvInt("FLASHMOE_BATCH_MT", 0));
-  params_.bulk_return = EnvInt("FLASHMOE_BULK_RETURN", 0) != 0;
   params_.gate_w = gate_dev;
   params_.act = act_;
   params_.topk_idx = topk_idx_;

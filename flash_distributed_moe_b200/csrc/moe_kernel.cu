@@ -397,9 +397,10 @@ __device__ __forceinline__ bool try_pop(const FdmoeParams& p, SmemCtl& sc, int q
   return true;
 }
 
-// The next task of this worker (single thread): queue 0 first; then a DISPATCH task unless enough
-// workers are dispatching already (across GPUs the links set the pace of the dispatch, a few workers
-// saturate them while the others feed the tensor cores); then a GATE tile; then queue 1.
+// The next task of this worker (single thread): a DISPATCH task first (everything else waits for
+// rows) unless enough workers are dispatching already (across GPUs the links set the pace of the
+// dispatch, a part of the workers saturates them while the others feed the tensor cores); then
+// queue 0; then a GATE tile; then queue 1.
 // Waits (bounded) while there is nothing to do and the rank's work is not finished.
 template <bool S>
 __device__ __forceinline__ FdmoeSlot next_task(const FdmoeParams& p, SmemCtl& sc, uint32_t gate_tiles) {
@@ -409,11 +410,11 @@ __device__ __forceinline__ FdmoeSlot next_task(const FdmoeParams& p, SmemCtl& sc
   uint32_t spins = 0;
   for (;;) {
     if (sc.abort) return exit_task();
-    if (try_pop<S>(p, sc, 0, out)) return out;
     if ((int32_t)ld_relaxed<false>(&ctl->q[2].avail) > 0 && ld_relaxed<false>(&ctl->disp_active) < (uint32_t)p.disp_conc) {
       if (atomicAdd(&ctl->disp_active, 1u) < (uint32_t)p.disp_conc && try_pop<false>(p, sc, 2, out)) return out;
       atomicSub(&ctl->disp_active, 1u);
     }
+    if (try_pop<S>(p, sc, 0, out)) return out;
     if (gate_tiles != 0u && ld_relaxed<false>(&ctl->gate_next) < gate_tiles) {
       const uint32_t g = atomicAdd(&ctl->gate_next, 1u);
       if (g < gate_tiles) {
@@ -1164,10 +1165,6 @@ __device__ __forceinline__ bool ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc,
                                                  ((size_t)token * p.K + slot) * p.H + n * FDMOE_TILE_N2 + h * 128);
   }
   const uint32_t tbase = taddr + ((uint32_t)(q * 32) << 16) + h * 128;
-  // Rows that go to another GPU may leave as bulk copies (one 128-byte copy per row and pass, issued by
-  // the row's lane from a linear staging row): the copy engine keeps more writes in flight over NVLink
-  // than the SM's store path does.
-  const bool bulk = p.bulk_return != 0 && __any_sync(0xffffffffu, remote);
 #pragma unroll
   for (int pass = 0; pass < 2; ++pass) {
 #pragma unroll
@@ -1178,25 +1175,10 @@ __device__ __forceinline__ bool ffn2_epilogue(const FdmoeParams& p, SmemCtl& sc,
 #pragma unroll
       for (int w = 0; w < 16; ++w)
         o[w] = pack_bf16(__uint_as_float(d[2 * w]) * wgt, __uint_as_float(d[2 * w + 1]) * wgt);
-      if (bulk) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v)
-          *reinterpret_cast<uint4*>(st + lane * 128 + ((c * 4 + v) << 4)) =
-              make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
-      } else {
-        stage_half_row(st, lane, c, o);
-      }
+      stage_half_row(st, lane, c, o);
     }
-    if (bulk) {
-      ptx::fence_proxy_async();  // the staged row (generic writes) before the copy engine reads it
-      if (myptr) ptx::bulk_store_1d(reinterpret_cast<uint8_t*>(myptr) + pass * 128, st + lane * 128, 128u);
-      ptx::bulk_commit_group();
-      ptx::bulk_wait_group_read0();  // the staging row may be overwritten
-    } else {
-      store_staged_rows(st, lane, myptr ? myptr + (unsigned long long)(pass * 128) : 0ull);
-    }
+    store_staged_rows(st, lane, myptr ? myptr + (unsigned long long)(pass * 128) : 0ull);
   }
-  if (bulk) ptx::bulk_wait_group0();  // the rows are written before the tile is handed on
   return remote;
 }
 

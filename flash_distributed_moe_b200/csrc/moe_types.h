@@ -146,8 +146,6 @@ typedef struct {
   int32_t gate_rows;    // tokens per GATE task: 32, 64 or 128 (rows of the 128-row MMA tile that are used)
   int32_t disp_conc;    // DISPATCH tasks worked on at a time
   int32_t batch_mt;     // m-tiles per publication batch; 0 = chosen from the token counts of the launch
-  int32_t bulk_return;  // 1: weighted rows for other GPUs leave the FFN2 epilogue as bulk copies
-  int32_t pad_params[3];
   int32_t mode;         // 0 full layer; 2 static tasks only (no gate)
   uint32_t expected_static;  // mode 2: tasks pre-filled by the host
   uint32_t epoch;       // launch counter (identical on all ranks)
