@@ -18,7 +18,11 @@ environment variable FLASH_MOE_ENABLED=1 is set.  Differences from the reference
     step, while leaving the step itself alone (the reference turns it into a no-op, which would
     break vLLM's own path for batches above the token bound);
   * `FLASH_MOE_MAX_TOKENS` (default 8192) bounds the tokens per call that go through the kernel;
-    larger batches use vLLM's block, like the reference's `num_tokens < maxTokens` test.
+    larger batches use vLLM's block, like the reference's `num_tokens < maxTokens` test;
+  * `FLASH_MOE_VERIFY=1` (a checking mode, not for production: it runs both implementations and
+    synchronises) makes every call also run vLLM's own block on a copy of the input and appends one
+    JSON line per call to the file `$FLASH_MOE_VERIFY_LOG.<pid>`: rows, rows whose relative L2 distance
+    to vLLM's result exceeds 2e-2, and the largest and the median of those distances.
 
 With expert parallelism every forward call is collective over the EP group: vLLM's data-parallel
 engines already run in lockstep for their own all-to-all (idle ranks run dummy batches).
@@ -53,6 +57,7 @@ def make_wrapper_class(base):
             self.maxTokens = int(os.environ.get("FLASH_MOE_MAX_TOKENS", "8192"))
             self.launcher = None
             self._flash_moe_topk = int(vllm_config.model_config.hf_text_config.num_experts_per_tok)
+            self._flash_moe_verify = os.environ.get("FLASH_MOE_VERIFY", "0") == "1"
 
         def _create_launcher(self) -> None:
             gate_w = self.gate.weight
@@ -91,10 +96,35 @@ def make_wrapper_class(base):
             if self.launcher is None:
                 self._create_launcher()
             tokens = hidden_states if hidden_states.is_contiguous() else hidden_states.contiguous()
+            theirs = super().forward(tokens.clone()) if self._flash_moe_verify else None
             self.launcher.launch(tokens, tokens)  # in place: output memory = input memory
+            if theirs is not None:
+                record_row_distances(tokens, theirs.reshape(tokens.shape))
             return tokens
 
     return FlashMoeWrapper
+
+
+VERIFY_ROW_TOLERANCE = 2e-2
+
+
+def row_distances(ours, theirs):
+    """Relative L2 distance of every row of `ours` to the same row of `theirs` (fp32, 1-D tensor)."""
+    a, b = ours.float(), theirs.float()
+    return (a - b).norm(dim=1) / b.norm(dim=1).clamp_min(1e-12)
+
+
+def record_row_distances(ours, theirs) -> None:
+    """Appends one JSON line about this call to `$FLASH_MOE_VERIFY_LOG.<pid>` (checking mode)."""
+    import json
+    path = os.environ.get("FLASH_MOE_VERIFY_LOG", "")
+    if not path or ours.shape[0] == 0:
+        return
+    d = row_distances(ours, theirs)
+    line = {"rows": int(d.numel()), "rows_beyond": int((d > VERIFY_ROW_TOLERANCE).sum().item()),
+            "max": float(d.max().item()), "median": float(d.median().item())}
+    with open(f"{path}.{os.getpid()}", "a") as f:
+        f.write(json.dumps(line) + "\n")
 
 
 def apply_flash_moe_patch() -> bool:

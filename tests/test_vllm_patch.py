@@ -45,6 +45,21 @@ def test_patch_reaches_a_freshly_started_process():
     assert "CHILD True Qwen3MoeSparseMoeBlock" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
+def test_checking_mode_records_row_distances(tmp_path, monkeypatch):
+    # FLASH_MOE_VERIFY=1: one JSON line per call with the rows beyond the relative distance of 2e-2
+    import json
+    monkeypatch.setenv("FLASH_MOE_VERIFY_LOG", str(tmp_path / "calls"))
+    theirs = torch.randn(6, 32)
+    ours = theirs.clone()
+    ours[1] *= 1.5      # far
+    ours[4] += 1e-4     # near
+    vllm_patch.record_row_distances(ours.to(torch.bfloat16).float(), theirs)
+    vllm_patch.record_row_distances(theirs[:0], theirs[:0])  # empty calls leave no line
+    lines = [json.loads(x) for x in open(f"{tmp_path / 'calls'}.{os.getpid()}")]
+    assert len(lines) == 1 and lines[0]["rows"] == 6 and lines[0]["rows_beyond"] == 1
+    assert 0.4 < lines[0]["max"] < 0.6 and lines[0]["median"] < vllm_patch.VERIFY_ROW_TOLERANCE
+
+
 class _Experts(torch.nn.Module):
     def __init__(self, w13, w2):
         super().__init__()

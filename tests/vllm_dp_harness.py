@@ -2,7 +2,7 @@
 that routes its MoE block through the launcher (twin of the reference's
 test/multiGPU/python/benchmark_dp.py:137-252,412-435 and flash_moe_patch.py:42-112).
 
-    python tests/vllm_dp_harness.py --dp 2 [--out result.json]
+    python tests/vllm_dp_harness.py --dp 2 [--mode tokens|verify] [--out result.json]
 
 One process per data-parallel rank (one GPU each), expert parallelism on, eager mode, no tokenizer.
 The model is written to a temporary directory with seeded weights (a checkpoint of a few MB; vLLM's
@@ -10,7 +10,11 @@ own dummy weights are so small that every logit is a tie), so greedy decoding is
 script runs the job twice, patch off and patch on, and compares the generated token ids: the first
 generated token of every prompt must agree, and at least 90 % of all generated tokens (after a
 first difference, caused by bf16 rounding of nearly tied logits, the two runs decode different
-histories).  Unlike the reference's patch, which falls back to vLLM's block when ep_size > 1
+histories).  `--mode verify` brings up the patched job only, in the patch's checking mode: every call
+of the MoE block runs vLLM's own block and the kernel on the same input inside the engine, and the
+script requires that the job generates its tokens and that at least 95 % of all rows of all calls lie
+within a relative L2 distance of 2e-2 of vLLM's rows (vLLM routes on bf16 logits, so a few per cent of
+the rows pick another last expert than the kernel's exact routing and differ more).  Unlike the reference's patch, which falls back to vLLM's block when ep_size > 1
 (flash_moe_patch.py:104), the patched run dispatches rows between the ranks inside the kernel.
 
 Exit codes: 0 agreement, 1 the token ids disagree, 77 vLLM itself could not run here, 78 the patched
@@ -86,8 +90,9 @@ def free_port() -> int:
         return s.getsockname()[1]
 
 
-def worker(dp_size, rank, port, model_dir, patched, prompts, max_tokens, queue):
+def worker(dp_size, rank, port, model_dir, patched, prompts, max_tokens, queue, extra_env=None):
     try:
+        os.environ.update(extra_env or {})
         os.environ.update({"VLLM_DP_RANK": str(rank), "VLLM_DP_RANK_LOCAL": str(rank), "VLLM_DP_SIZE": str(dp_size),
                            "VLLM_DP_MASTER_IP": "127.0.0.1", "VLLM_DP_MASTER_PORT": str(port),
                            "HF_HUB_OFFLINE": "1", "TRANSFORMERS_OFFLINE": "1", "VLLM_LOGGING_LEVEL": "WARNING",
@@ -118,11 +123,11 @@ def worker(dp_size, rank, port, model_dir, patched, prompts, max_tokens, queue):
         queue.put({"rank": rank, "ok": False, "error": f"{type(e).__name__}: {e}", "trace": traceback.format_exc()[-3000:]})
 
 
-def run_job(dp_size, model_dir, patched, prompts, max_tokens, timeout_s=900):
+def run_job(dp_size, model_dir, patched, prompts, max_tokens, timeout_s=900, extra_env=None):
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
     port = free_port()
-    procs = [ctx.Process(target=worker, args=(dp_size, r, port, model_dir, patched, prompts, max_tokens, queue))
+    procs = [ctx.Process(target=worker, args=(dp_size, r, port, model_dir, patched, prompts, max_tokens, queue, extra_env))
              for r in range(dp_size)]
     for p in procs:
         p.start()
@@ -141,6 +146,35 @@ def run_job(dp_size, model_dir, patched, prompts, max_tokens, timeout_s=900):
     return results
 
 
+def verify_mode(args, model_dir, prompts) -> int:
+    """The patched job alone, in the patch's checking mode; returns the exit code."""
+    import glob
+    log = os.path.join(tempfile.mkdtemp(prefix="flash_moe_verify_"), "calls")
+    res = run_job(args.dp, model_dir, True, prompts, args.max_tokens, args.job_timeout,
+                  {"FLASH_MOE_VERIFY": "1", "FLASH_MOE_VERIFY_LOG": log})
+    bad = [r for r in res.values() if not r.get("ok")]
+    if len(res) < args.dp or bad:
+        print(json.dumps({"status": "vllm could not run", "patched": True, "dp": args.dp,
+                          "errors": [b.get("error") for b in bad], "trace": (bad[0].get("trace") if bad else "")}))
+        return 78
+    calls = [json.loads(line) for f in glob.glob(log + ".*") for line in open(f) if line.strip()]
+    rows = sum(c["rows"] for c in calls)
+    beyond = sum(c["rows_beyond"] for c in calls)
+    generated = sum(len(t) for r in res.values() for t in r["tokens"])
+    report = {"status": "ok", "mode": "verify", "dp": args.dp, "processes_with_calls": len(glob.glob(log + ".*")),
+              "calls": len(calls), "rows": rows, "rows_beyond_2e-2": beyond,
+              "median_of_call_medians": (sorted(c["median"] for c in calls)[len(calls) // 2] if calls else None),
+              "max_row_distance": max((c["max"] for c in calls), default=None), "tokens_generated": generated,
+              "init_s": max(r["init_s"] for r in res.values()), "gen_s": max(r["gen_s"] for r in res.values())}
+    print(json.dumps(report))
+    if args.out:
+        with open(args.out, "w") as f:
+            json.dump(report, f)
+    want = len(prompts) * args.max_tokens if args.dp <= len(prompts) else None
+    ok = len(calls) > 0 and rows > 0 and beyond <= 0.05 * rows and (want is None or generated == want)
+    return 0 if ok else 1
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--dp", type=int, default=1)
@@ -148,14 +182,18 @@ def main():
     ap.add_argument("--input-len", type=int, default=24)
     ap.add_argument("--max-tokens", type=int, default=6)
     ap.add_argument("--out", default="")
+    ap.add_argument("--mode", choices=("tokens", "verify"), default="tokens")
+    ap.add_argument("--job-timeout", type=int, default=900)
     args = ap.parse_args()
     import numpy as np
     rng = np.random.RandomState(0)
     prompts = [rng.randint(3, VOCAB, size=args.input_len).tolist() for _ in range(args.prompts)]
     model_dir = make_model_dir(tempfile.mkdtemp(prefix="qwen3moe_tiny_"))
+    if args.mode == "verify":
+        sys.exit(verify_mode(args, model_dir, prompts))
     runs = {}
     for patched in (False, True):
-        res = run_job(args.dp, model_dir, patched, prompts, args.max_tokens)
+        res = run_job(args.dp, model_dir, patched, prompts, args.max_tokens, args.job_timeout)
         bad = [r for r in res.values() if not r.get("ok")]
         if len(res) < args.dp or bad:
             print(json.dumps({"status": "vllm could not run", "patched": patched, "dp": args.dp,
