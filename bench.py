@@ -12,7 +12,9 @@ tokens per GPU; with N > 1 the experts are sharded over the ranks (expert parall
 tokens per GPU stay fixed (weak scaling).  `--skew zipf` biases the gate so that expert popularity
 follows Zipf(1.2).  Before anything is timed, every rank checks a sample of its tokens against the
 CPU oracle (top-k indices exact, output within max-abs 2e-2 / rel-L2 1e-2).  Rank 0 prints ONE JSON
-line.
+line.  At N = 1 its `cpu_baseline` holds the reference project's CPU MoE on all host threads (`value`),
+the same code on one thread (`single_thread`) and a plain-torch restatement of the same math on the
+host cores (`torch_cpu`), each timed on a bounded sample of the step's tokens.
 
 `--impl reference` times the reference project's own CPU MoE (oracle/_ref when it was built from
 the reference sources, else the C restatement under oracle/) on the host cores, on a bounded sample
@@ -228,14 +230,31 @@ def cpu_baseline_leg(shape, gate, w13, w2, x, budget_s=12.0):
     gf = gate.float().cpu().numpy()
     w13f = w13.float().cpu().numpy()
     w2f = w2.float().cpu().numpy()
-    xs = x[:max(4 * threads, 256)].float().cpu().numpy()
+    xs = x[:4096].float().cpu().numpy()
     probe = min(threads, xs.shape[0])
     _, dt = cpu_reference_run(oracle, xs[:probe], gf, w13f, w2f, shape.topk, threads)
     per_round = max(dt, 1e-3)
     n = int(min(xs.shape[0], max(probe, probe * int(budget_s / per_round))))
     _, dt = cpu_reference_run(oracle, xs[:n], gf, w13f, w2f, shape.topk, threads)
+    # the same code on one thread (tokens are independent, the cost per token is constant)
+    n1 = max(1, min(32, int(1.5 / max(per_round, 1e-3))))
+    _, dt1 = cpu_reference_run(oracle, xs[:n1], gf, w13f, w2f, shape.topk, 1)
+    # the plain-torch restatement of the same math on the host cores (library GEMMs, expert by expert)
+    from oracle.torch_moe import torch_moe
+    tg, t13, t2 = (torch.from_numpy(a) for a in (gf, w13f, w2f))
+    xt = x[:min(x.shape[0], 2048)].float().cpu()
+    torch_moe(xt[:64], tg, t13, t2, shape.topk)
+    t0 = time.perf_counter()
+    torch_moe(xt, tg, t13, t2, shape.topk)
+    dtt = time.perf_counter() - t0
     return {"value": n / dt, "unit": "tokens/s", "cores": threads, "kind": oracle.kind,
-            "sample": f"first {n} tokens of the step's batch, fp32, all host threads, {dt:.1f} s"}
+            "sample": f"first {n} tokens of the step's batch, fp32, all host threads, {dt:.1f} s",
+            "single_thread": {"value": n1 / dt1, "unit": "tokens/s", "cores": 1,
+                              "sample": f"first {n1} tokens, {dt1:.1f} s"},
+            "torch_cpu": {"value": xt.shape[0] / dtt, "unit": "tokens/s", "cores": torch.get_num_threads(),
+                          "kind": "port",
+                          "sample": f"first {xt.shape[0]} tokens of the step's batch through the plain-torch "
+                                    f"restatement (fp32, library GEMMs per expert), {dtt:.2f} s"}}
 
 
 def run_reference_arm(args, shape):

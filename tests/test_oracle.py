@@ -143,3 +143,21 @@ def test_bf16_weight_variant_equals_widened_weights(port):
     bits = lambda t: t.view(torch.int16).numpy().view(np.uint16)  # noqa: E731
     out2, tw2, ti2 = port.full_moe_bf16_weights(x, tl.f32(gate), bits(w13), bits(w2), s.topk, threads=2)
     assert np.array_equal(out, out2) and np.array_equal(tw, tw2) and np.array_equal(ti, ti2)
+
+
+def test_torch_restatement_agrees_with_the_port(port):
+    # the plain-torch CPU path that the benchmark times beside the reference's own CPU code
+    import torch
+    from oracle.torch_moe import torch_moe
+    s = synth.TINY
+    gate, w13, w2 = synth.make_weights(s, std=0.05)
+    x = synth.make_tokens(s, 200, seed=3)
+    out, tw, ti, _, _ = port.full_moe(tl.f32(x), tl.f32(gate), tl.f32(w13), tl.f32(w2), s.topk, stages=True)
+    got, gw, gi = torch_moe(x.float(), gate.float(), w13.float(), w2.float(), s.topk)
+    logits = port.gemm_nt(tl.f32(x), tl.f32(gate))
+    srt = -np.sort(-logits, axis=1)[:, :s.topk + 1]
+    clear = (srt[:, :-1] - srt[:, 1:]).min(axis=1) > 1e-5      # rows whose routing no rounding can change
+    assert clear.mean() > 0.9
+    assert (gi.numpy()[clear] == ti[clear]).all()
+    np.testing.assert_allclose(gw.numpy()[clear], tw[clear], atol=1e-6)
+    np.testing.assert_allclose(got.numpy()[clear], out[clear], atol=1e-5)
