@@ -266,16 +266,17 @@ def run_reference_arm(args, shape):
     oracle = cpu_oracle.best_oracle()
     threads = oracle.max_threads()
     gate, w13, w2 = synth.make_weights(shape, seed=0)
-    x = synth.make_tokens(shape, max(threads * 4, 64), seed=0)
+    x = synth.make_tokens(shape, min(args.tokens, 2048), seed=0)
     if args.skew == "zipf":
         gate, x, _ = synth.zipf_routing(shape, gate, x, s=1.2, seed=0)
     gf, w13f, w2f, xf = [t.float().numpy() for t in (gate, w13, w2, x)]
     # bounded sample per step: calibrate one round of `threads` tokens, then size the step so that the
     # whole run stays within about two minutes
-    _, dt = cpu_reference_run(oracle, xf[:threads], gf, w13f, w2f, shape.topk, threads)
+    probe = min(threads, xf.shape[0])
+    _, dt = cpu_reference_run(oracle, xf[:probe], gf, w13f, w2f, shape.topk, threads)
     total_steps = args.steps + args.warmup
     per_step_budget = max(0.5, 120.0 / max(total_steps, 1))
-    n = int(min(xf.shape[0], max(threads, threads * int(per_step_budget / max(dt, 1e-3)))))
+    n = int(min(xf.shape[0], max(probe, probe * int(per_step_budget / max(dt, 1e-3)))))
     for _ in range(args.warmup):
         cpu_reference_run(oracle, xf[:n], gf, w13f, w2f, shape.topk, threads)
     t0 = time.perf_counter()
