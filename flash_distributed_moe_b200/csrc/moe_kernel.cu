@@ -1,20 +1,22 @@
 // The persistent MoE-layer kernel for sm_100a and its thin C ABI.
 //
-// One CTA per SM, every CTA a worker that takes tasks from the rank's two task queues (queue 0
-// before queue 1) or claims the next GATE tile, and overlaps these kinds of work:
-//   GATE    token tile: gate GEMM on tcgen05, top-k, softmax, row reservation in the owners'
-//           expert buffers, then the dispatch of the tile's rows: every token row is brought
-//           into shared memory once and goes out as K bulk copies, one per selected expert,
-//           into the owner's buffer (local, or a peer's over NVLink).  Tokens whose leading
-//           logits are nearly tied are recomputed by a GATEFIX task with fp32 FMAs in the
-//           reference's accumulation order, so the selection is the reference's;
-//   FFN1/2  128-row expert tiles on tcgen05 with TMEM accumulators fed by TMA (SwiGLU epilogue;
-//           routing-weight epilogue stored on the token's home rank).  The sender whose rows
-//           complete a batch of m-tiles of an expert publishes the batch's FFN1 tiles on the
-//           owner's queue; what is left when every rank has gated is published by the owner's
-//           GATED task, expert by expert;
-//   COMBINE token group: ordered sum of the K weighted rows, published by whoever delivers the
-//           group's last row.
+// One CTA per SM, every CTA a worker that takes tasks from the rank's three task queues (queue 0:
+// FFN2, COMBINE, GATEFIX, GATED; queue 1: FFN1; queue 2: DISPATCH) or claims the next GATE tile, and
+// overlaps these kinds of work:
+//   GATE     token tile: gate GEMM on tcgen05, top-k, softmax; indices and weights go to global
+//            memory.  Tokens whose leading logits are nearly tied are recomputed by a GATEFIX task
+//            with fp32 FMAs in the reference's accumulation order, so the selection is the
+//            reference's;
+//   DISPATCH the rows of one GATE tile: rows are reserved in the owners' expert buffers, every
+//            token row is brought into shared memory once and goes out as K bulk copies, one per
+//            selected expert, into the owner's buffer (local, or a peer's over NVLink);
+//   FFN1/2   128-row expert tiles on tcgen05 with TMEM accumulators fed by TMA (SwiGLU epilogue;
+//            routing-weight epilogue stored on the token's home rank).  The sender whose rows
+//            complete a batch of m-tiles of an expert publishes the batch's FFN1 tiles on the
+//            owner's queue; what is left when every rank has gated is published by the owner's
+//            GATED task, expert by expert;
+//   COMBINE  token group: ordered sum of the K weighted rows, published by whoever delivers the
+//            group's last row.
 // Cross-GPU traffic is plain stores, bulk stores and relaxed system-scope atomics into peers'
 // symmetric buffers.  System-scope fences cost microseconds on this hardware (several times more
 // while host copies are in flight), so they are issued once per task that talked to a peer, never
@@ -261,8 +263,6 @@ __device__ __noinline__ void raise_error(const FdmoeParams& p, SmemCtl& sc, uint
   atomicExch(&ctl->closed, 2u);
 }
 
-// Bounded mbarrier wait.  Returns false (after raising the error) on timeout
-// or when another role of this CTA has aborted.
 // Where a role gave up waiting (diagnostics, one record per CTA and warp):
 // {error code, byte offset of the barrier inside SmemCtl, parity, microseconds waited}.
 __device__ __noinline__ void record_stuck(const FdmoeParams& p, SmemCtl& sc, uint64_t* bar, uint32_t parity,
@@ -315,12 +315,12 @@ __device__ __forceinline__ bool wait_idle(const FdmoeParams& p, SmemCtl& sc, uin
 }
 
 // ------------------------------------------------------------- task queues
-// A rank has two queues.  Producers (this rank's workers and, for queue slots in the symmetric
+// A rank has three queues.  Producers (this rank's workers and, for queue slots in the symmetric
 // arena, its peers) take `n` consecutive tickets with one atomic add on head, fill the slots,
 // publish each with a store of ticket + 1 after one fence, and then add `n` to the queue's count of
 // available tasks.  Consumers (this rank's workers only) first take one unit of that count (giving
 // it back if there was none), and only then a ticket from tail: a consumer never holds a ticket
-// for a task that does not exist yet, so it can always turn to the other queue, and no
+// for a task that does not exist yet, so it can always turn to another queue, and no
 // compare-and-swap loop serialises the workers.
 // `S`: the queue belongs to a peer (system-scope atomics and fence), else to this GPU.
 template <bool S, class Gen>
@@ -786,10 +786,10 @@ __device__ __forceinline__ uint32_t dispatch_rows_per_stage(int H) {
 // Then the TMA warp brings the token rows (contiguous in the token matrix) into the pipeline stages;
 // one thread per (row of the stage, slot) writes the row's sideband and sends the row to the expert's
 // owner as one bulk copy (local, or a peer's memory over NVLink), so a token row is read once and
-// written K times.  While the copies of a stage are in flight the thread finishes the stage before
-// it: waits until its copy of that stage is written, counts the row as landed on its owner (one
-// fence first) and publishes the FFN1 tiles of a batch this completes; then the stage goes back to
-// the TMA warp.  Returns false when the group has to give up.
+// written K times.  A stage goes back to the TMA warp as soon as the copies out of it have read
+// their rows.  When all copies of the task are written, one thread per expert counts the task's rows
+// as landed on their owner (one fence first) and publishes the FFN1 tiles of every batch this
+// completes.  Returns false when the group has to give up.
 template <bool S>
 __device__ __noinline__ bool dispatch_task(const FdmoeParams& p, SmemCtl& sc, uint8_t* stage, uint32_t& stage_it,
                                            int etid, int ewarp, int lane, uint32_t t0, uint32_t nt) {
