@@ -11,7 +11,8 @@
 //   * gate weights [E,H], FFN1 weights [E/world, 2I, H] (rows 0..I-1 gate
 //     projection, I..2I-1 up projection), FFN2 weights [E/world, H, I], tokens and
 //     output [T,H], all contiguous; `output` may alias `tokens`;
-//   * Launch is asynchronous on `stream`; one Launch in flight per launcher;
+//   * Launch is asynchronous on `stream`; one Launch in flight per launcher; with worldSize == 1 it
+//     only enqueues work on `stream` and can be captured into a CUDA graph, with peers it cannot;
 //   * with worldSize > 1, CreateLauncher, every Launch and DestroyLauncher are
 //     collective over the ranks; tokensNum may differ per rank and may be 0;
 //   * errors are return codes (cudaSuccess == 0); a configuration that does not

@@ -147,3 +147,37 @@ def test_block_wrapper_in_place():
         o = tl.f32(got.cpu())
         assert np.abs(o - ref).max() <= tl.MAX_ABS and tl.rel_l2(o, ref) <= tl.REL_L2
     wrapper.launcher.destroy()
+
+
+def test_single_gpu_launch_replays_from_a_cuda_graph():
+    # On one GPU a launch is a memset and a kernel launch on the caller's stream, so it can be captured
+    # into a CUDA graph (the reference's launch cannot: its micro-benchmark says so,
+    # test/singleGPU/python/qwen3MoeMicroBenchmark.py:84); the replay reads whatever the captured
+    # token buffer holds at that time.
+    s = synth.TINY
+    gate, w13, w2 = synth.make_weights(s, std=0.05)
+    port = cpu_oracle.PortOracle()
+    g, a, b = gate.cuda(), w13.cuda(), w2.cuda()
+    launcher = MoeKernelLauncher()
+    launcher.create(g, a, b, 64, launcher.getDistributedUniqueId(empty=True), 0, 1, topk=s.topk)
+    try:
+        x_dev = synth.make_tokens(s, 48, seed=60).cuda()
+        out_dev = torch.empty_like(x_dev)
+        launcher.launch(x_dev, out_dev)  # first launch outside the capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            launcher.launch(x_dev, out_dev)
+        for seed in (61, 62, 63):
+            x = synth.make_tokens(s, 48, seed=seed)
+            x_dev.copy_(x)
+            out_dev.zero_()
+            graph.replay()
+            torch.cuda.synchronize()
+            assert launcher.last_status() == (0, 0)
+            ref = port.full_moe(tl.f32(x), tl.f32(gate), tl.f32(w13), tl.f32(w2), s.topk)
+            tl.assert_close_bf16(tl.f32(out_dev.cpu()), ref, f"graph replay, seed {seed}")
+        del graph
+    finally:
+        torch.cuda.synchronize()
+        launcher.destroy()
