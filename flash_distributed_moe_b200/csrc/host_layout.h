@@ -54,15 +54,32 @@ struct Geometry {
 // Slots of any task queue of a rank: at least every task one launch can publish there, so
 // that a slot is never reused within a launch.  Tile tasks of the rank's experts (FFN1 in one
 // queue, FFN2 in the other), COMBINE tasks (one per group of combine_group tokens), GATEFIX
-// tasks (two tokens each, every token in the worst case), the GATED round, and DISPATCH tasks (one
-// per GATE tile of at least 32 tokens).
-inline uint32_t QueueCapacity(const Geometry& g, int grid) {
+// tasks (two tokens each, every token in the worst case, rounded up per GATE tile), the GATED round,
+// and DISPATCH tasks (one per GATE tile of at least 32 tokens).
+inline uint64_t WorstCaseQueueTasks(const Geometry& g) {
   const uint64_t rows_max = std::min<uint64_t>((uint64_t)g.max_tokens_sum * g.K, (uint64_t)g.El * g.cap_rows);
   const uint64_t mtiles = rows_max / FDMOE_TILE_M + g.El;
   const uint64_t tiles = mtiles * (uint64_t)std::max(g.I / FDMOE_TILE_N1, g.H / FDMOE_TILE_N2);
-  const uint64_t tasks = tiles + (uint64_t)g.max_tokens_max / std::max(1, g.combine_group) +
-                         (uint64_t)g.max_tokens_max / 2 + (uint64_t)grid + 1024;
-  return NextPow2(tasks + 1024);
+  const uint64_t gate_tiles = (uint64_t)g.max_tokens_max / 32 + 1;
+  return tiles + (uint64_t)g.max_tokens_max / std::max(1, g.combine_group) + 1 +
+         (uint64_t)g.max_tokens_max / 2 + gate_tiles + 1;
+}
+
+inline uint32_t QueueCapacity(const Geometry& g, int grid) {
+  return NextPow2(WorstCaseQueueTasks(g) + (uint64_t)grid + 2048);
+}
+
+// Derived sizes once the token bounds, the shape and combine_group are known: rows of a local expert's
+// buffer (an expert receives at most one row per token of any rank), m-tiles per expert, queue
+// capacity.  Returns false when the expert buffers would hold more rows than a dispatch word can
+// address (28 bits).
+inline bool FinishGeometry(Geometry& g, int grid) {
+  const uint64_t cap = AlignUp((size_t)std::max<int64_t>(g.max_tokens_sum, 1), FDMOE_TILE_M);
+  if ((uint64_t)g.El * cap >= (1ull << 28)) return false;
+  g.cap_rows = (int)cap;
+  g.MT = g.cap_rows / FDMOE_TILE_M;
+  g.queue_cap = QueueCapacity(g, grid);
+  return true;
 }
 
 inline size_t CombineGroups(const Geometry& g) {
@@ -86,6 +103,7 @@ inline ArenaLayout MakeLayout(const Geometry& g) {
   L.ffn2_done = off;
   off += AlignUp((size_t)g.El * g.MT * 4, 128);
   L.zero_end = off;
+  off = AlignUp(off, 1024);  // the regions from here on start on 1024-byte boundaries
   for (int q = 0; q < 3; ++q) {
     L.slots[q] = off;
     off += AlignUp((size_t)g.queue_cap * sizeof(FdmoeSlot), 1024);

@@ -224,15 +224,12 @@ cudaError_t MoeKernelLauncher::Init(const void* gateW, const void* w13, const vo
     g_.max_tokens_max = std::max(g_.max_tokens_max, h.max_tokens);
     g_.max_tokens_sum += h.max_tokens;
   }
-  g_.cap_rows = (int)AlignUp((size_t)std::max<int64_t>(g_.max_tokens_sum, 1), FDMOE_TILE_M);
-  g_.MT = g_.cap_rows / FDMOE_TILE_M;
   g_.combine_group = std::max(1, EnvInt("FLASHMOE_COMBINE_GROUP", 8));
-  if ((uint64_t)g_.El * g_.cap_rows >= (1ull << 28)) {
+  if (!FinishGeometry(g_, grid_)) {
     MOE_ERROR_LOG("maxTokens=%d: more expert-buffer rows than a dispatch word can address", maxTokens);
     FreeAll();
     return cudaErrorUnknown;
   }
-  g_.queue_cap = QueueCapacity(g_, grid_);
   layout_ = MakeLayout(g_);
 
   // ---- allocations

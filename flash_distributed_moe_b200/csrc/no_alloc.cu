@@ -132,10 +132,8 @@ extern "C" int FlashMoeLaunchNoAlloc(const void* gateWeights, const void* ffn1Ex
   g.world = 1;
   g.max_tokens_local = g.max_tokens_max = std::max(tokensNum, 1);
   g.max_tokens_sum = g.max_tokens_max;
-  g.cap_rows = (int)AlignUp((size_t)g.max_tokens_sum, FDMOE_TILE_M);
-  g.MT = g.cap_rows / FDMOE_TILE_M;
   g.combine_group = 8;
-  g.queue_cap = QueueCapacity(g, d->grid);
+  if (!FinishGeometry(g, d->grid)) return (int)cudaErrorInvalidValue;
   const ArenaLayout L = MakeLayout(g);
   // regions the launcher allocates separately follow the arena inside the same array
   size_t off = AlignUp(L.total, 1024);
