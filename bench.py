@@ -23,6 +23,7 @@ of the same workload per step.
 from __future__ import annotations
 
 import argparse
+import atexit
 import json
 import os
 import statistics
@@ -177,20 +178,25 @@ class SharedWeights:
                 np.lib.format.open_memmap(p, mode="w+", dtype=np.uint16, shape=shp).flush()
         barrier()
         self.maps = [np.load(p, mmap_mode="r+") for p in self.paths]
+        atexit.register(self._unlink)  # a rank that dies before close() must not leave gigabytes behind
         for m, t in zip(self.maps, (w13, w2)):
             m[rank * el:(rank + 1) * el] = t.cpu().view(torch.int16).numpy().view(np.uint16)
             m.flush()
         barrier()
 
+    def _unlink(self):
+        # (removing a file that other ranks still have mapped leaves their mappings valid)
+        for p in self.paths:
+            try:
+                os.remove(p)
+            except OSError:
+                pass
+
     def close(self, barrier):
         self.maps = None
         barrier()
         if self.rank == 0:
-            for p in self.paths:
-                try:
-                    os.remove(p)
-                except OSError:
-                    pass
+            self._unlink()
 
 
 def parity_check(shape, launcher, shared, gate, x, out, n_check, threads):
