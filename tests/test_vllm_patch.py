@@ -113,3 +113,20 @@ def test_wrapper_class_runs_the_layer_in_place_and_falls_back_above_max_tokens(m
     assert wrapper.fallback_calls == 1
     wrapper.launcher.destroy()
     wrapper.launcher = None
+
+
+def test_harness_checkpoint_is_a_loadable_qwen3_moe_model(tmp_path):
+    # the seeded one-layer checkpoint the vLLM harness writes: a Hugging Face Qwen3-MoE model that loads
+    # without missing weights and whose greedy next token is well defined (no tied logits)
+    transformers = pytest.importorskip("transformers")
+    import vllm_dp_harness as harness
+    path = harness.make_model_dir(str(tmp_path / "model"))
+    model, info = transformers.AutoModelForCausalLM.from_pretrained(path, dtype=torch.bfloat16, output_loading_info=True)
+    assert not info["missing_keys"] and not info["unexpected_keys"], info
+    assert model.config.num_experts == harness.EXPERTS and model.config.num_experts_per_tok == harness.TOPK
+    ids = torch.from_numpy(np.random.RandomState(0).randint(3, harness.VOCAB, size=(4, 16)))
+    with torch.no_grad():
+        logits = model(ids).logits[:, -1].float()
+    assert torch.isfinite(logits).all()
+    best = logits.topk(2, dim=-1).values
+    assert ((best[:, 0] - best[:, 1]) > 0).all()
