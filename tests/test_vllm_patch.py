@@ -130,3 +130,29 @@ def test_harness_checkpoint_is_a_loadable_qwen3_moe_model(tmp_path):
     assert torch.isfinite(logits).all()
     best = logits.topk(2, dim=-1).values
     assert ((best[:, 0] - best[:, 1]) > 0).all()
+
+
+def test_oracle_equals_the_hugging_face_qwen3_moe_block(tmp_path):
+    # The layer the launcher replaces, as the model library itself computes it (transformers'
+    # Qwen3MoeSparseMoeBlock, fp32, CPU) against the CPU oracle on the harness's checkpoint: pins the
+    # meaning of the weight layout (gate projection in rows 0..I-1 of w13) and of the routing weights
+    # (softmax renormalised over the selected experts) at the boundary where the operator is dropped in.
+    transformers = pytest.importorskip("transformers")
+    from safetensors.torch import load_file
+    import vllm_dp_harness as harness
+    path = harness.make_model_dir(str(tmp_path / "model"))
+    model = transformers.AutoModelForCausalLM.from_pretrained(path, dtype=torch.float32)
+    block = model.model.layers[0].mlp
+    x = torch.randn(40, harness.HIDDEN, generator=torch.Generator().manual_seed(3))
+    with torch.no_grad():
+        y = block(x.unsqueeze(0))
+    y = (y[0] if isinstance(y, tuple) else y).reshape(40, harness.HIDDEN)
+    t = load_file(os.path.join(path, "model.safetensors"))
+    p = "model.layers.0.mlp."
+    gate = t[p + "gate.weight"].float()
+    w13 = torch.stack([torch.cat([t[p + f"experts.{e}.gate_proj.weight"], t[p + f"experts.{e}.up_proj.weight"]], 0)
+                       for e in range(harness.EXPERTS)]).float()
+    w2 = torch.stack([t[p + f"experts.{e}.down_proj.weight"] for e in range(harness.EXPERTS)]).float()
+    cpu_oracle.build()
+    ref = cpu_oracle.PortOracle().full_moe(tl.f32(x), tl.f32(gate), tl.f32(w13), tl.f32(w2), harness.TOPK)
+    np.testing.assert_allclose(y.numpy(), ref, atol=1e-4, rtol=1e-4)
